@@ -1,0 +1,436 @@
+// extern "C" entry points declared in include/cats_b200.h: argument checks, grid sizing and
+// launches.  No allocation, no device synchronisation (except cats_read_counters), no exit().
+#include "../../include/cats_b200.h"
+
+#include <string.h>
+
+#include "cats_kernels.cuh"
+
+namespace {
+
+using namespace cats;
+
+thread_local cudaError_t g_last_cuda = cudaSuccess;
+
+struct DevInfo {
+  int sms = 0;
+  int max_smem_optin = 0;
+};
+
+// Per-device properties, queried once per device (no allocation involved).
+const DevInfo& dev_info() {
+  static DevInfo info[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (info[dev].sms == 0) {
+    int sms = 0, smem = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    info[dev].max_smem_optin = smem;
+    info[dev].sms = sms > 0 ? sms : 148;
+  }
+  return info[dev];
+}
+
+int esize(int dtype) { return dtype == CATS_F32 ? 4 : 2; }
+int vecn(int dtype) { return dtype == CATS_F32 ? 4 : 8; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(int B, int H, int I, int dtype) {
+  if (dtype != CATS_F32 && dtype != CATS_F16 && dtype != CATS_BF16) return CATS_ERR_DTYPE;
+  if (B < 1 || B > kMaxB || H < 1 || I < 1) return CATS_ERR_SHAPE;
+  if (H % vecn(dtype) != 0) return CATS_ERR_SHAPE;
+  return CATS_OK;
+}
+
+int check_ws(void* ws, size_t ws_bytes, int H, int I, WsPtrs* p) {
+  if (!ws) return CATS_ERR_NULL;
+  if (!aligned16(ws)) return CATS_ERR_ALIGN;
+  if (ws_layout(ws, H, I, p) > ws_bytes) return CATS_ERR_WORKSPACE;
+  return CATS_OK;
+}
+
+int cuda_status(cudaError_t e) {
+  if (e == cudaSuccess) return CATS_OK;
+  g_last_cuda = e;
+  return CATS_ERR_CUDA;
+}
+
+// Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while
+// its predecessor drains; every kernel here calls griddepcontrol.wait before touching data.
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                   cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+int batch_tile(int B) { return B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : B <= 8 ? 8 : 16; }
+
+// Call F<T, BT>::run(args...) for the runtime (dtype, B).
+#define CATS_DISPATCH_BT(T, BT_, FN, ...)         \
+  switch (BT_) {                                  \
+    case 1: return FN<T, 1>(__VA_ARGS__);         \
+    case 2: return FN<T, 2>(__VA_ARGS__);         \
+    case 4: return FN<T, 4>(__VA_ARGS__);         \
+    case 8: return FN<T, 8>(__VA_ARGS__);         \
+    default: return FN<T, 16>(__VA_ARGS__);       \
+  }
+#define CATS_DISPATCH(dtype, BT_, FN, ...)                                     \
+  do {                                                                         \
+    if ((dtype) == CATS_F32) { CATS_DISPATCH_BT(float, BT_, FN, __VA_ARGS__) } \
+    if ((dtype) == CATS_F16) { CATS_DISPATCH_BT(__half, BT_, FN, __VA_ARGS__) } \
+    CATS_DISPATCH_BT(__nv_bfloat16, BT_, FN, __VA_ARGS__)                      \
+  } while (0)
+
+// ---- grid sizing --------------------------------------------------------------------------
+int gate_segments(int I) {
+  int g = dev_info().sms * 2;
+  if (g > kMaxSeg) g = kMaxSeg;
+  const int by_rows = (I + 15) / 16;  // at least ~16 rows (two per warp) per CTA
+  if (g > by_rows) g = by_rows;
+  return g < 1 ? 1 : g;
+}
+
+int updown_ctas(int I) {
+  int g = dev_info().sms * 2;
+  const int by_rows = (I + 7) / 8;
+  if (g > by_rows) g = by_rows;
+  return g < 1 ? 1 : g;
+}
+
+template <typename T, int BT>
+cudaError_t run_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, float thr,
+                     void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
+  const int nseg = gate_segments(I);
+  const int rmax = (I + nseg - 1) / nseg;
+  const size_t smem = sizeof(float) * (size_t)rmax * BT;
+  return launch(k_gate<T, BT>, dim3(nseg), dim3(kThreads), smem, st, (const T*)x, (const T*)Wg,
+                ws, B, H, I, thr, (T*)gate_dense, flag_dense);
+}
+
+template <typename T, int BT, int MODE>
+cudaError_t run_updown_mode(const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
+                            int H, int I, void* out, int out_mode, void* resid, void* x_next,
+                            const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
+  const int G = updown_ctas(I);
+  const int cap = (I + G - 1) / G;
+  const size_t smem = (size_t)(cap + kRU) * (sizeof(int) + sizeof(float) * BT);
+  return launch(k_updown<T, BT, MODE>, dim3(G), dim3(kThreads), smem, st, (const T*)x,
+                (const T*)Wu, (const T*)WdT, ws, B, H, I, cap, (T*)out, out_mode, (T*)resid,
+                (T*)x_next, (const T*)norm_w, eps, (T*)inter_dense);
+}
+
+template <typename T, int BT>
+cudaError_t run_updown(int mode, const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
+                       int H, int I, void* out, int out_mode, void* resid, void* x_next,
+                       const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
+  if (mode == 1)
+    return run_updown_mode<T, BT, 1>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
+                                     eps, inter_dense, st);
+  if (mode == 2)
+    return run_updown_mode<T, BT, 2>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
+                                     eps, inter_dense, st);
+  return run_updown_mode<T, BT, 3>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
+                                   eps, inter_dense, st);
+}
+
+template <typename T, int BT>
+cudaError_t run_rows_gemv(const void* xs, const void* W, int B, int K, int R, void* out,
+                          cudaStream_t st) {
+  int g = dev_info().sms * 4;
+  const int need = (R + kWarps * 2 - 1) / (kWarps * 2);
+  if (g > need) g = need;
+  return launch(k_rows_gemv<T, BT>, dim3(g), dim3(kThreads), 0, st, (const T*)xs, (const T*)W, B,
+                K, R, (T*)out);
+}
+
+cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, int dtype,
+                    float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
+  CATS_DISPATCH(dtype, batch_tile(B), run_gate, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense,
+                st);
+}
+
+cudaError_t do_updown(int mode, const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
+                      int H, int I, int dtype, void* out, int out_mode, void* resid, void* x_next,
+                      const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
+  CATS_DISPATCH(dtype, batch_tile(B), run_updown, mode, x, Wu, WdT, ws, B, H, I, out, out_mode,
+                resid, x_next, norm_w, eps, inter_dense, st);
+}
+
+int check_out_mode(int out_mode, const void* out, const void* resid, const void* x_next) {
+  if (out_mode != CATS_OUT_STORE && out_mode != CATS_OUT_ACC_F32) return CATS_ERR_MODE;
+  if (out_mode == CATS_OUT_ACC_F32 && (resid || x_next)) return CATS_ERR_MODE;
+  if (x_next && !resid) return CATS_ERR_MODE;
+  if (!out && !resid) return CATS_ERR_NULL;
+  if (out && !aligned16(out)) return CATS_ERR_ALIGN;
+  return CATS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cats_abi_version(void) { return 1; }
+
+const char* cats_status_string(int status) {
+  switch (status) {
+    case CATS_OK: return "ok";
+    case CATS_ERR_DTYPE: return "unknown dtype (expected CATS_F32, CATS_F16 or CATS_BF16)";
+    case CATS_ERR_SHAPE:
+      return "bad shape (need 1 <= B <= 16, H >= 1, I >= 1 and rows that are a whole number of "
+             "16-byte vectors)";
+    case CATS_ERR_ALIGN: return "pointer is not 16-byte aligned";
+    case CATS_ERR_NULL: return "required pointer is NULL";
+    case CATS_ERR_WORKSPACE: return "workspace is smaller than cats_workspace_bytes(B, H, I)";
+    case CATS_ERR_CUDA: return "CUDA error at launch";
+    case CATS_ERR_MODE: return "unsupported mode or flag combination";
+    default: return "unknown status";
+  }
+}
+
+const char* cats_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
+
+int cats_sm_count(void) { return dev_info().sms; }
+
+size_t cats_workspace_bytes(int B, int H, int I) {
+  (void)B;
+  if (H < 1 || I < 1) return 0;
+  return ws_layout(nullptr, H, I, nullptr);
+}
+
+int cats_workspace_init(void* ws, size_t ws_bytes, void* stream) {
+  if (!ws) return CATS_ERR_NULL;
+  return cuda_status(cudaMemsetAsync(ws, 0, ws_bytes, static_cast<cudaStream_t>(stream)));
+}
+
+int cats_gate(const void* x, const void* Wg, void* ws, size_t ws_bytes, int B, int H, int I,
+              int dtype, float threshold, void* gate_dense, uint8_t* flag_dense, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wg) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wg)) return CATS_ERR_ALIGN;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  return cuda_status(do_gate(x, Wg, p, B, H, I, dtype, threshold, gate_dense, flag_dense,
+                             static_cast<cudaStream_t>(stream)));
+}
+
+int cats_compact(const void* values, const uint8_t* flags, void* ws, size_t ws_bytes, int B,
+                 int H, int I, int dtype, float threshold, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!values) return CATS_ERR_NULL;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (dtype == CATS_F32)
+    e = launch(k_compact<float>, dim3(1), dim3(1024), 0, st, (const float*)values, flags, p, B, I,
+               threshold);
+  else if (dtype == CATS_F16)
+    e = launch(k_compact<__half>, dim3(1), dim3(1024), 0, st, (const __half*)values, flags, p, B,
+               I, threshold);
+  else
+    e = launch(k_compact<__nv_bfloat16>, dim3(1), dim3(1024), 0, st,
+               (const __nv_bfloat16*)values, flags, p, B, I, threshold);
+  return cuda_status(e);
+}
+
+int cats_up(const void* x, const void* Wu, void* ws, size_t ws_bytes, int B, int H, int I,
+            int dtype, void* inter_dense, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wu) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wu)) return CATS_ERR_ALIGN;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  return cuda_status(do_updown(1, x, Wu, nullptr, p, B, H, I, dtype, nullptr, CATS_OUT_STORE,
+                               nullptr, nullptr, nullptr, 0.f, inter_dense,
+                               static_cast<cudaStream_t>(stream)));
+}
+
+int cats_down(const void* WdT, void* ws, size_t ws_bytes, int B, int H, int I, int dtype,
+              void* out, int out_mode, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!WdT || !out) return CATS_ERR_NULL;
+  if (!aligned16(WdT)) return CATS_ERR_ALIGN;
+  if ((s = check_out_mode(out_mode, out, nullptr, nullptr))) return s;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  return cuda_status(do_updown(2, nullptr, nullptr, WdT, p, B, H, I, dtype, out, out_mode,
+                               nullptr, nullptr, nullptr, 0.f, nullptr,
+                               static_cast<cudaStream_t>(stream)));
+}
+
+int cats_updown(const void* x, const void* Wu, const void* WdT, void* ws, size_t ws_bytes,
+                int B, int H, int I, int dtype, void* out, int out_mode, void* resid,
+                void* x_next, const void* norm_weight, float eps, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wu || !WdT) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wu) || !aligned16(WdT)) return CATS_ERR_ALIGN;
+  if ((s = check_out_mode(out_mode, out, resid, x_next))) return s;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, out_mode, resid, x_next,
+                               norm_weight, eps, nullptr, static_cast<cudaStream_t>(stream)));
+}
+
+int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, void* ws,
+             size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
+             int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
+             void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wg || !Wu || !WdT) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(WdT)) return CATS_ERR_ALIGN;
+  if ((s = check_out_mode(out_mode, out, resid, x_next))) return s;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st);
+  if (e != cudaSuccess) return cuda_status(e);
+  return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, out_mode, resid, x_next,
+                               norm_weight, eps, nullptr, st));
+}
+
+int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const void* const* WdT,
+                   const float* thresholds, void* x_io, void* x_tmp, void* resid, void* ws,
+                   size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (L < 1) return CATS_ERR_SHAPE;
+  if (!Wg || !Wu || !WdT || !thresholds || !x_io || !x_tmp || !resid) return CATS_ERR_NULL;
+  if (!aligned16(x_io) || !aligned16(x_tmp) || !aligned16(resid)) return CATS_ERR_ALIGN;
+  for (int l = 0; l < L; ++l) {
+    if (!Wg[l] || !Wu[l] || !WdT[l]) return CATS_ERR_NULL;
+    if (!aligned16(Wg[l]) || !aligned16(Wu[l]) || !aligned16(WdT[l])) return CATS_ERR_ALIGN;
+  }
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  void* cur = x_io;
+  void* nxt = x_tmp;
+  for (int l = 0; l < L; ++l) {
+    cudaError_t e = do_gate(cur, Wg[l], p, B, H, I, dtype, thresholds[l], nullptr, nullptr, st);
+    if (e != cudaSuccess) return cuda_status(e);
+    e = do_updown(3, cur, Wu[l], WdT[l], p, B, H, I, dtype, nullptr, CATS_OUT_STORE, resid, nxt,
+                  nullptr, eps, nullptr, st);
+    if (e != cudaSuccess) return cuda_status(e);
+    void* t = cur;
+    cur = nxt;
+    nxt = t;
+  }
+  if (cur != x_io)
+    return cuda_status(cudaMemcpyAsync(x_io, cur, (size_t)B * H * esize(dtype),
+                                       cudaMemcpyDeviceToDevice, st));
+  return CATS_OK;
+}
+
+int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int dtype, void* out,
+                    void* stream) {
+  // rows of Wd [H, I] have length I: the vector-width rule applies to I here
+  int s = check_common(B, I, H, dtype);
+  if (s) return s;
+  if (!inter || !Wd || !out) return CATS_ERR_NULL;
+  if (!aligned16(inter) || !aligned16(Wd)) return CATS_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto go = [&]() -> cudaError_t {
+    CATS_DISPATCH(dtype, batch_tile(B), run_rows_gemv, inter, Wd, B, I, H, out, st);
+  };
+  return cuda_status(go());
+}
+
+int cats_tail(const void* y, void* resid, void* x_next, const void* norm_weight, float eps, int B,
+              int H, int dtype, void* stream) {
+  if (dtype != CATS_F32 && dtype != CATS_F16 && dtype != CATS_BF16) return CATS_ERR_DTYPE;
+  if (B < 1 || H < 1) return CATS_ERR_SHAPE;
+  if (!y || !resid) return CATS_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (dtype == CATS_F32)
+    e = launch(k_tail<float>, dim3(B), dim3(kThreads), 0, st, (const float*)y, (float*)resid,
+               (float*)x_next, (const float*)norm_weight, eps, H);
+  else if (dtype == CATS_F16)
+    e = launch(k_tail<__half>, dim3(B), dim3(kThreads), 0, st, (const __half*)y, (__half*)resid,
+               (__half*)x_next, (const __half*)norm_weight, eps, H);
+  else
+    e = launch(k_tail<__nv_bfloat16>, dim3(B), dim3(kThreads), 0, st, (const __nv_bfloat16*)y,
+               (__nv_bfloat16*)resid, (__nv_bfloat16*)x_next, (const __nv_bfloat16*)norm_weight,
+               eps, H);
+  return cuda_status(e);
+}
+
+int cats_transpose(const void* src, void* dst, int rows, int cols, int dtype, void* stream) {
+  if (dtype != CATS_F32 && dtype != CATS_F16 && dtype != CATS_BF16) return CATS_ERR_DTYPE;
+  if (rows < 1 || cols < 1) return CATS_ERR_SHAPE;
+  if (!src || !dst) return CATS_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  if (esize(dtype) == 4)
+    k_transpose<uint32_t><<<grid, block, 0, st>>>((const uint32_t*)src, (uint32_t*)dst, rows, cols);
+  else
+    k_transpose<uint16_t><<<grid, block, 0, st>>>((const uint16_t*)src, (uint16_t*)dst, rows, cols);
+  return cuda_status(cudaGetLastError());
+}
+
+int cats_read_counters(const void* ws, int* n_active, int* device_status, void* stream) {
+  if (!ws) return CATS_ERR_NULL;
+  // header and segment counts sit at the start of the workspace whatever (H, I) are
+  static_assert(sizeof(int) * kHdrInts % 256 == 0, "header must keep 256-byte alignment");
+  int host[kHdrInts + kMaxSeg];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(host, ws, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_status(e);
+  int nseg = host[HDR_NSEG];
+  if (nseg < 0) nseg = 0;
+  if (nseg > kMaxSeg) nseg = kMaxSeg;
+  long long n = 0;
+  for (int c = 0; c < nseg; ++c) n += host[kHdrInts + c];
+  if (n_active) *n_active = (int)n;
+  if (device_status) *device_status = host[HDR_STATUS];
+  return CATS_OK;
+}
+
+int cats_export_list(const void* ws, size_t ws_bytes, int B, int H, int I, int dtype,
+                     int64_t* idx_out, void* val_out, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  WsPtrs p;
+  if ((s = check_ws(const_cast<void*>(ws), ws_bytes, H, I, &p))) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int g = (I + kThreads - 1) / kThreads;
+  if (g > dev_info().sms) g = dev_info().sms;
+  cudaError_t e;
+  if (dtype == CATS_F32)
+    e = launch(k_export<float>, dim3(g), dim3(kThreads), 0, st, p, B, I, (long long*)idx_out,
+               (float*)val_out);
+  else if (dtype == CATS_F16)
+    e = launch(k_export<__half>, dim3(g), dim3(kThreads), 0, st, p, B, I, (long long*)idx_out,
+               (__half*)val_out);
+  else
+    e = launch(k_export<__nv_bfloat16>, dim3(g), dim3(kThreads), 0, st, p, B, I,
+               (long long*)idx_out, (__nv_bfloat16*)val_out);
+  return cuda_status(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,223 @@
+// Shared device helpers for the CATS sparse-MLP decode kernels (sm_100a).
+//
+// Everything here is CUDA-core code on purpose: batch-1 decode is a GEMV, one FMA per weight
+// element read from HBM, so the kernels are shaped around bytes in flight per SM (16-byte
+// streaming loads, many independent loads per lane) and not around tensor cores.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cats {
+
+constexpr int kThreads = 256;        // threads per CTA of every streaming kernel
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxSeg = 1024;        // upper bound on stage-1 segments (= stage-1 CTAs)
+constexpr int kMaxB = 16;            // largest batch the kernels are instantiated for
+constexpr int kHdrInts = 64;         // workspace header size in ints
+
+// header slots
+enum { HDR_NACTIVE = 0, HDR_TICKET = 1, HDR_STATUS = 2, HDR_NSEG = 3 };
+
+// Resolved workspace pointers (see ws_layout).
+struct WsPtrs {
+  int* hdr;          // [kHdrInts]
+  int* seg_count;    // [kMaxSeg]   active neurons found by stage-1 CTA c
+  float* acc32;      // [kMaxB * H] split-K accumulators, zero between calls
+  int* seg_idx;      // [I]         segment c's ordered neuron list starts at row0(c)
+  float* seg_gate;   // [I * B]     gate value per list entry and token (0 = token inactive)
+  int* flat_idx;     // [I]         globally ordered list (written by stage 2 / compact)
+  float* h;          // [I * B]     gate * up per flat list entry and token
+};
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Layout is a function of (H, I) only: the batch dimension is always provisioned for kMaxB so
+// one workspace serves any B without moving the zero-initialised accumulator region.
+__host__ __device__ inline size_t ws_layout(void* base, int H, int I, WsPtrs* p) {
+  size_t off = 0;
+  char* b = static_cast<char*>(base);
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off = align_up(off + bytes, 256);
+    return o;
+  };
+  size_t o_hdr = take(sizeof(int) * kHdrInts);
+  size_t o_cnt = take(sizeof(int) * kMaxSeg);
+  size_t o_acc = take(sizeof(float) * (size_t)kMaxB * H);
+  size_t o_sidx = take(sizeof(int) * (size_t)I);
+  size_t o_sgate = take(sizeof(float) * (size_t)I * kMaxB);
+  size_t o_fidx = take(sizeof(int) * (size_t)I);
+  size_t o_h = take(sizeof(float) * (size_t)I * kMaxB);
+  if (p) {
+    p->hdr = reinterpret_cast<int*>(b + o_hdr);
+    p->seg_count = reinterpret_cast<int*>(b + o_cnt);
+    p->acc32 = reinterpret_cast<float*>(b + o_acc);
+    p->seg_idx = reinterpret_cast<int*>(b + o_sidx);
+    p->seg_gate = reinterpret_cast<float*>(b + o_sgate);
+    p->flat_idx = reinterpret_cast<int*>(b + o_fidx);
+    p->h = reinterpret_cast<float*>(b + o_h);
+  }
+  return off;
+}
+
+// First row of stage-1 segment c out of nseg over I rows (balanced, ascending).
+__host__ __device__ inline int seg_row0(int c, int nseg, int I) {
+  return (int)(((long long)c * I) / nseg);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16-byte vectors of the three element types
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct VecT;
+
+template <>
+struct VecT<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+
+template <>
+struct VecT<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+template <>
+struct VecT<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) {
+    return __float2bfloat16_rn(v);
+  }
+};
+
+// Streaming 16-byte load of weight data: read-only path, no L1 allocation so that the
+// activations (re-read for every row) stay resident in L1.
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p));
+  return v;
+}
+
+// Compiler-only fence: keeps every load issued above it ahead of the arithmetic below it, so a
+// lane really has all of them in flight before it waits for the first one.
+__device__ __forceinline__ void issue_fence() { asm volatile("" ::: "memory"); }
+
+// Vector reduction into global fp32 accumulators (one L2 atomic transaction per 16 bytes).
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// Programmatic dependent launch: wait until every grid this one depends on has completed and
+// its memory is visible (no-op when the launch carried no programmatic dependency) ...
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// ... and allow the next grid in the stream to be scheduled once all CTAs got here.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+// Active rule of the reference: a neuron is dead when |v| <= t (ugly_utils.py:897), so it is
+// active when that comparison is false — NaN stays active and propagates, as it does there.
+__device__ __forceinline__ bool is_active(float v, float t) { return !(fabsf(v) <= t); }
+
+// ---------------------------------------------------------------------------------------------
+// Dot products of up to two weight rows with the B activation vectors, one warp per call.
+//   w0 / w1 : row starts (w1 may be nullptr), xs : [B, H] activations
+//   acc[r][b] receives this lane's partial sums (caller reduces across the warp).
+// Per outer step every lane issues 2*U independent 16-byte loads before the first FMA.
+// ---------------------------------------------------------------------------------------------
+// FMA one 16-byte vector of up to two rows against the B activation vectors.
+template <typename T, int BT>
+__device__ __forceinline__ void fma_vec2(const uint4& a, const uint4& b, const uint4* px, int nvec,
+                                         int v, int B, float (&acc)[2][BT]) {
+  using V = VecT<T>;
+  constexpr int N = V::N;
+  float fa[N], fb[N];
+  V::unpack(a, fa);
+  V::unpack(b, fb);
+#pragma unroll
+  for (int t = 0; t < BT; ++t) {
+    if (t < B) {
+      float fx[N];
+      V::unpack(__ldg(px + (size_t)t * nvec + v), fx);
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        acc[0][t] = fmaf(fa[i], fx[i], acc[0][t]);
+        acc[1][t] = fmaf(fb[i], fx[i], acc[1][t]);
+      }
+    }
+  }
+}
+
+template <typename T, int BT, int U>
+__device__ __forceinline__ void warp_dot2(const T* __restrict__ w0, const T* __restrict__ w1,
+                                          const T* __restrict__ xs, int B, int H, int lane,
+                                          float (&acc)[2][BT]) {
+  constexpr int N = VecT<T>::N;
+  const int nvec = H / N;
+  const uint4* p0 = reinterpret_cast<const uint4*>(w0);
+  // a missing second row re-reads the first (its sums are discarded by the caller): keeps the
+  // main loop free of per-load predicates
+  const uint4* p1 = reinterpret_cast<const uint4*>(w1 ? w1 : w0);
+  const uint4* px = reinterpret_cast<const uint4*>(xs);
+  int v0 = 0;
+  for (; v0 + 32 * U <= nvec; v0 += 32 * U) {  // full steps: unconditional loads
+    uint4 a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[u] = ldg_stream(p0 + v0 + u * 32 + lane);
+#pragma unroll
+    for (int u = 0; u < U; ++u) b[u] = ldg_stream(p1 + v0 + u * 32 + lane);
+    issue_fence();
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      fma_vec2<T, BT>(a[u], b[u], px, nvec, v0 + u * 32 + lane, B, acc);
+  }
+  for (int v = v0 + lane; v < nvec; v += 32) {  // ragged tail
+    const uint4 a = ldg_stream(p0 + v);
+    const uint4 b = ldg_stream(p1 + v);
+    fma_vec2<T, BT>(a, b, px, nvec, v, B, acc);
+  }
+}
+
+}  // namespace cats

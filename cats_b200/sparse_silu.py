@@ -1,0 +1,298 @@
+"""CATS MLP module with the reference's interface, running decode on the sm_100a kernels.
+
+Mirrors the inference-relevant part of experiments/models/sparse_silu/ugly_utils.py:
+``SparseSiLU`` (:80-92), ``{Llama,Mistral}SparseSiluMLP`` (:469-622, :807-959) with the same
+constructor keywords, attributes (``is_profile``, ``sp_method``, ``dead_threshold``, ``wdown_t``,
+``kill_sparse_swish_outputs``, ``use_relu``, ``is_stats`` ...) and ``forward(x, sp_mask=None)``,
+and the model-level helpers the reference's bench scripts call (``apply_sparse_silu_mlp``,
+``enable_sparse_silu``, ``activate_stats``, ``load_act_hist``, ``set_sparse_threshold``, ...;
+experiments/bench_sparse_inference_llama.py:38-77).
+
+Dispatch of ``forward`` when ``is_profile`` is set (as in the reference, :877-904):
+  decode (x.shape[1] == 1), sp_method 1 or 2 -> the CUDA path (``ops.mlp``); the reference calls
+        flash_gemv.flag_gemv_gemv_inner_bf16 / gemv_gemv_triton here
+  decode, sp_method 0                         -> dense thresholded PyTorch (the reference's own
+        comparison branch, kept verbatim as the in-module reference)
+  prefill (x.shape[1] > 1)                    -> dense thresholded PyTorch
+The training-time extras of the reference module (regularisation terms, trainer callbacks, SVD
+predictor) are not part of the decode path and are not reproduced.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+
+class SparseSiLU(nn.SiLU):
+    """SiLU whose outputs with |v| <= threshold are zeroed (ugly_utils.py:80-92)."""
+
+    def __init__(self, threshold):
+        super().__init__()
+        self.threshold = threshold
+        self.m = nn.Threshold(self.threshold, 0)
+
+    def set_new_threshold(self, threshold):
+        self.threshold = threshold
+        self.m = nn.Threshold(threshold, 0)
+
+    def forward(self, x):
+        act = super().forward(x)
+        return self.m(act) - self.m(-act)
+
+
+def _cfg(config, name, default=None):
+    if isinstance(config, dict):
+        return config.get(name, default)
+    return getattr(config, name, default)
+
+
+class CatsSparseSiluMLP(nn.Module):
+    """SiLU-gated MLP with CATS thresholding.  ``config`` needs ``hidden_size`` and
+    ``intermediate_size`` (an HF LlamaConfig / MistralConfig or a dict)."""
+
+    def __init__(self, config, *args, **kwargs):
+        super().__init__()
+        self.config = config
+        self.hidden_size = _cfg(config, "hidden_size")
+        self.intermediate_size = _cfg(config, "intermediate_size")
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+        self.act_fn = nn.SiLU()
+
+        self.swish_outputs = None
+        self.relu = nn.ReLU()
+        self.is_profile = False
+        self.sp_method = 1
+        self.wdown_t = None
+
+        self.kill_sparse_swish_outputs = False
+        self.dead_percentage = 0
+        self.is_stats = False
+        self.visit_counts = 0
+
+        self.dead_threshold = kwargs.pop("dead_threshold", 0)
+        self.use_sparse_regularization = kwargs.pop("use_sparse_regularization", True)
+        self.regularization_type = kwargs.pop("regularization_type", "L1 regularization")
+        self.regularization_threshold = kwargs.pop("regularization_threshold", 0.5)
+        self.use_relu = kwargs.pop("use_relu", False)
+        self.activation_norm = None
+
+        # activation histograms: 1000 edges = -inf, 998 points on [-1, 1], +inf (ugly_utils.py:826-833)
+        self.is_collect_histogram = False
+        num_bins = 1000
+        bins = torch.linspace(-1, 1, num_bins - 2)
+        self.histogram_bins = torch.cat([torch.tensor([-torch.inf]), bins, torch.tensor([torch.inf])])
+        self.pre_act_hist_counts = torch.zeros(num_bins - 1)
+        self.abs_post_act_hist_counts = torch.zeros(num_bins - 1)
+        self.post_act_hist_counts = torch.zeros(num_bins - 1)
+        self.t = 0
+        self.count = 0
+        self.agg_sparsity = 0
+
+        self.sparse_act_fn = SparseSiLU(threshold=self.dead_threshold)
+
+    # ---- statistics (host-side, as in the reference) ----------------------------------------
+    def activate_stats(self, is_collect_histogram: bool = True):
+        self.is_stats = True
+        self.dead_percentage = 0
+        self.visit_counts = 0
+        self.is_collect_histogram = is_collect_histogram
+        self.histogram_counts = torch.zeros(2000)
+
+    def deactivate_stats(self):
+        self.is_stats = False
+
+    def collect_stats(self, pre_activation, post_activation):
+        pre_activation = pre_activation.float().cpu().detach()
+        post_activation = post_activation.float().cpu().detach()
+        self.pre_act_hist_counts += torch.histogram(pre_activation, bins=self.histogram_bins)[0]
+        self.post_act_hist_counts += torch.histogram(torch.abs(post_activation),
+                                                     bins=self.histogram_bins)[0]
+
+    # ---- forward ------------------------------------------------------------------------------
+    def _dense_thresholded(self, x):
+        post_act = self.act_fn(self.gate_proj(x))
+        dead_neurons = post_act.abs() <= self.dead_threshold
+        post_act[dead_neurons] = 0
+        return self.down_proj(post_act * self.up_proj(x))
+
+    def packed_down(self) -> torch.Tensor:
+        """down_proj.weight as WdT (I, H).  Uses ``wdown_t`` when the caller set it the way the
+        reference bench does (bench_sparse_inference_llama.py:76), else packs and caches."""
+        w = self.wdown_t
+        if w is not None and w.is_contiguous() and w.device == self.down_proj.weight.device:
+            return w
+        return ops.packed_wdt(self.down_proj.weight)
+
+    def _cuda_decode(self, x):
+        return ops.mlp(x, self.gate_proj.weight, self.up_proj.weight, self.packed_down(),
+                       float(self.dead_threshold))
+
+    def forward(self, x, sp_mask: Optional[torch.Tensor] = None):
+        if sp_mask is not None:
+            return self.down_proj(self.sparse_act_fn(self.gate_proj(x) * sp_mask) * self.up_proj(x))
+
+        if self.is_profile:
+            if x.shape[1] == 1 and self.sp_method in (1, 2):
+                return self._cuda_decode(x)
+            return self._dense_thresholded(x)
+
+        if self.use_relu:
+            post_act = self.relu(self.gate_proj(x))
+            self.count += 1
+            if self.is_stats:
+                dead_neurons = post_act == 0
+                dead_percentage = dead_neurons.float().mean()
+                agg_sparsity = dead_neurons.all(dim=0).float().mean()
+                self.dead_percentage = (self.dead_percentage * self.visit_counts + dead_percentage) / (
+                    self.visit_counts + 1)
+                self.agg_sparsity = (self.agg_sparsity * self.visit_counts + agg_sparsity) / (
+                    self.visit_counts + 1)
+                self.visit_counts += 1
+            return self.down_proj(post_act * self.up_proj(x))
+
+        self.count += 1
+        pre_act = self.gate_proj(x)
+        post_act = self.act_fn(pre_act)
+        if self.kill_sparse_swish_outputs:
+            dead_neurons = post_act.abs() <= self.dead_threshold
+            dead_percentage = dead_neurons.float().mean()
+            agg_sparsity = dead_neurons.all(dim=0).float().mean()
+            if self.is_stats:
+                self.dead_percentage = (self.dead_percentage * self.visit_counts + dead_percentage) / (
+                    self.visit_counts + 1)
+                self.agg_sparsity = (self.agg_sparsity * self.visit_counts + agg_sparsity) / (
+                    self.visit_counts + 1)
+                self.visit_counts += 1
+                self.a = dead_percentage
+                if self.is_collect_histogram and self._collect_this(pre_act):
+                    self.collect_stats(pre_act, post_act)
+            post_act[dead_neurons] = 0
+        return self.down_proj(post_act * self.up_proj(x))
+
+    def _collect_this(self, pre_act) -> bool:
+        return True
+
+
+class LlamaSparseSiluMLP(CatsSparseSiluMLP):
+    """Reference: ugly_utils.py:807-959."""
+
+
+class MistralSparseSiluMLP(CatsSparseSiluMLP):
+    """Reference: ugly_utils.py:469-622 (skips histogram collection on all-padding batches)."""
+
+    def _collect_this(self, pre_act) -> bool:
+        return bool(pre_act.eq(0).float().mean() < 0.99)
+
+
+# ---- model-level helpers (the reference's bench scripts import these with `import *`) ----------
+def _layers(model):
+    return model.model.layers
+
+
+def get_mlp_class(model):
+    """Mistral models get MistralSparseSiluMLP, everything else the Llama class — the reference's
+    rule (ugly_utils.py:64-66, utils/utils.py:11-22), decided here from the config's model_type."""
+    mt = str(getattr(getattr(model, "config", None), "model_type", "")).lower()
+    return MistralSparseSiluMLP if "mistral" in mt else LlamaSparseSiluMLP
+
+
+def apply_sparse_silu_mlp(model, config, use_sparse_regularization: bool = False):
+    """Swap every layer's MLP for the CATS module, sharing the three nn.Linear layers
+    (ugly_utils.py:119-131)."""
+    SparseMLP = get_mlp_class(model)
+    for layer in _layers(model):
+        original_mlp = layer.mlp
+        new_mlp = SparseMLP(config, use_sparse_regularization=use_sparse_regularization)
+        new_mlp.gate_proj = original_mlp.gate_proj
+        new_mlp.up_proj = original_mlp.up_proj
+        new_mlp.down_proj = original_mlp.down_proj
+        layer.mlp = new_mlp
+
+
+def _sparse_mlps(model):
+    for i, layer in enumerate(_layers(model)):
+        if isinstance(layer.mlp, CatsSparseSiluMLP):
+            yield i, layer.mlp
+
+
+def activate_stats(model, is_collect_histogram: bool = True):
+    for _, mlp in _sparse_mlps(model):
+        mlp.activate_stats(is_collect_histogram=is_collect_histogram)
+
+
+def deactivate_stats(model):
+    for _, mlp in _sparse_mlps(model):
+        mlp.deactivate_stats()
+
+
+def enable_sparse_silu(model):
+    for _, mlp in _sparse_mlps(model):
+        mlp.kill_sparse_swish_outputs = True
+
+
+def disable_sparse_silu(model):
+    for _, mlp in _sparse_mlps(model):
+        mlp.kill_sparse_swish_outputs = False
+
+
+def print_dead_neuron_stats(model):
+    total, sparsity_list = 0.0, []
+    for i, mlp in _sparse_mlps(model):
+        dead = float(mlp.dead_percentage) * 100
+        sparsity_list.append(dead)
+        total += dead
+        print(f"layer {i} sparsity: {dead:.3f}%  agg sparsity: {float(mlp.agg_sparsity) * 100:.3f}%")
+    mean = total / max(1, len(sparsity_list))
+    print(f"Total sparsity: {mean: .3f}%")
+    return mean, sparsity_list
+
+
+def get_threshold(bin_edges: torch.Tensor, histogram_counts: torch.Tensor, sparsity_level: float):
+    """Bin edge at which the normalised histogram's CDF crosses ``sparsity_level``
+    (ugly_utils.py:236-245; note that, as there, the counts tensor is normalised in place)."""
+    assert len(bin_edges.shape) == len(histogram_counts.shape) == 1, \
+        "bin_edges and histogram are expected to be 1-dimensional."
+    histogram_counts /= histogram_counts.sum()
+    threshold_idx = torch.searchsorted(histogram_counts.cumsum(0), sparsity_level, side="right")
+    return bin_edges[threshold_idx]
+
+
+def set_sparse_threshold(model, sparsity_level: float, use_relu: bool = False):
+    """Per-layer threshold from the collected |post-activation| histogram (ugly_utils.py:257-273)."""
+    for _, mlp in _sparse_mlps(model):
+        if not mlp.is_stats:
+            continue
+        if use_relu:
+            mlp.sparse_act_fn = nn.ReLU()
+            mlp.use_relu = True
+        else:
+            mlp.dead_threshold = get_threshold(mlp.histogram_bins, mlp.post_act_hist_counts,
+                                               sparsity_level)
+            mlp.sparse_act_fn.set_new_threshold(mlp.dead_threshold)
+            mlp.regularization_threshold = mlp.dead_threshold * 1.2
+
+
+def save_act_hist(model, filename: str):
+    """{layer: (bins, pre_counts, post_counts)} via torch.save (ugly_utils.py:399-413)."""
+    os.makedirs(os.path.dirname(filename) or ".", exist_ok=True)
+    act_dict = {}
+    for i, mlp in _sparse_mlps(model):
+        if mlp.is_stats:
+            act_dict[i] = (mlp.histogram_bins, mlp.pre_act_hist_counts, mlp.post_act_hist_counts)
+    torch.save(act_dict, filename)
+
+
+def load_act_hist(model, filename: str):
+    """Inverse of save_act_hist; reads the reference's histogram files (ugly_utils.py:416-433)."""
+    assert os.path.exists(filename), f"{filename} does not exist when loading the activation histogram."
+    act_dict = torch.load(filename)
+    for i, mlp in _sparse_mlps(model):
+        if mlp.is_stats:
+            mlp.histogram_bins, mlp.pre_act_hist_counts, mlp.post_act_hist_counts = act_dict[i]

@@ -1,0 +1,199 @@
+/*
+ * cats_b200.h — C ABI of the B200 (sm_100a) CATS sparse-MLP decode kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, allocates nothing,
+ * never synchronises the device and never terminates the process.  The return value is a
+ * status code (CATS_OK == 0; negative values are argument errors detected on the host before
+ * any launch; CATS_ERR_CUDA reports a failed launch).  `cats_status_string` turns it into text.
+ *
+ * Tensor layouts (row-major, contiguous):
+ *   x        [B, H]   activations, B = batch * seq (decode: seq == 1), 1 <= B <= 16
+ *   Wg, Wu   [I, H]   nn.Linear.weight layout of gate_proj / up_proj (one neuron per row)
+ *   WdT      [I, H]   down_proj.weight transposed: intermediate-major, one neuron per row
+ *   Wd       [H, I]   down_proj.weight as stored by nn.Linear (dense fallback only)
+ *   out      [B, H]
+ * All rows must be 16-byte aligned: base pointers 16-byte aligned and H * sizeof(element) a
+ * multiple of 16 (H % 8 == 0 for fp16/bf16, H % 4 == 0 for fp32).
+ *
+ * Semantics replaced (reference = ScalingIntelligence/CATS):
+ *   out = Wd * ( mask(SiLU(Wg x)) * (Wu x) ),  mask keeps v where |v| > threshold (strict) and
+ *   zeroes it otherwise — experiments/models/sparse_silu/ugly_utils.py:896-899.
+ */
+#ifndef CATS_B200_H_
+#define CATS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of x / weights / out */
+enum { CATS_F32 = 0, CATS_F16 = 1, CATS_BF16 = 2 };
+
+/* status codes */
+enum {
+  CATS_OK = 0,
+  CATS_ERR_DTYPE = -1,      /* unknown dtype enum */
+  CATS_ERR_SHAPE = -2,      /* B, H or I out of range, or H not a multiple of the 16-byte vector */
+  CATS_ERR_ALIGN = -3,      /* a pointer is not 16-byte aligned */
+  CATS_ERR_NULL = -4,       /* a required pointer is NULL */
+  CATS_ERR_WORKSPACE = -5,  /* workspace too small for (B, H, I) */
+  CATS_ERR_CUDA = -6,       /* CUDA runtime reported an error at launch; see cats_last_cuda_error */
+  CATS_ERR_MODE = -7        /* unknown mode / flag combination */
+};
+
+/* how cats_down / cats_updown / cats_mlp deliver the result */
+enum {
+  CATS_OUT_STORE = 0,     /* out[B,H] (element type = dtype) is overwritten                        */
+  CATS_OUT_ACC_F32 = 1    /* out[B,H] is fp32 and the result is ADDED to it (caller pre-zeroes),   */
+                          /* the convention of the reference's atomic ops                           */
+};
+
+/* ABI version of this header (bumped when a signature changes). */
+int cats_abi_version(void);
+
+/* Text for a status code. */
+const char* cats_status_string(int status);
+
+/* Text of the CUDA error behind the most recent CATS_ERR_CUDA on the calling thread. */
+const char* cats_last_cuda_error(void);
+
+/* Number of SMs of the current device (the persistent grids are sized from it). */
+int cats_sm_count(void);
+
+/*
+ * Workspace.  One workspace serves every call with batch <= B, hidden <= H, intermediate <= I
+ * made in stream order on one stream; it holds the compacted active-neuron list, the per-neuron
+ * gate values, fp32 split-K accumulators and a self-resetting completion ticket.  It has to be
+ * cleared once with cats_workspace_init before first use; afterwards the kernels leave it clean.
+ * Replaces the per-call cudaMalloc/cudaFree of two scratch buffers in
+ * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:2351-2354, 2402-2403.
+ */
+size_t cats_workspace_bytes(int B, int H, int I);
+int cats_workspace_init(void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Stage 1 — fused gate GEMV + SiLU + |v| > threshold + warp-ballot compaction.
+ * Streams all of Wg once.  Leaves in the workspace the ordered list of neurons that are active
+ * for at least one of the B tokens and, per list entry and token, the fp32 gate value (0 where
+ * that token's own mask is off).  Optional dense outputs, either may be NULL:
+ *   gate_dense [B, I] (dtype)  SiLU(Wg x) of every neuron, rounded to dtype
+ *   flag_dense [B, I] (uint8)  1 where |SiLU(Wg x)| > threshold
+ * Replaces fuse_gemv_flag_local (flash_gemv/flash_gemv/flash_gemv.py:21-22;
+ * fuse_gemv_cmp_cuda.cu:1292-1486, 2083-2117) and the stage-1 launches of
+ * flag_gemv_gemv_inner* (fuse_gemv_cmp_cuda.cu:2369, 2446, 2523).
+ */
+int cats_gate(const void* x, const void* Wg, void* ws, size_t ws_bytes, int B, int H, int I,
+              int dtype, float threshold, void* gate_dense, uint8_t* flag_dense, void* stream);
+
+/*
+ * Build the workspace's active list from a dense gate tensor instead of stage 1.
+ *   values [B, I] (dtype); flags [B, I] uint8 or NULL.
+ * With flags == NULL a neuron is active for token b when |values[b,i]| > threshold, otherwise
+ * when flags[b,i] != 0 (threshold ignored).  H is the hidden size of the stage-2/3 calls that
+ * will consume the list (it fixes the workspace layout).  Serves the reference entry points that receive a
+ * precomputed SiLU(x Wg): gemv_gemv_triton (flash_gemv/flash_gemv/__init__.py:45-48),
+ * fuse_flag_gemv_local and atomic_gemv (flash_gemv/flash_gemv/flash_gemv.py:24-28).
+ */
+int cats_compact(const void* values, const uint8_t* flags, void* ws, size_t ws_bytes, int B,
+                 int H, int I, int dtype, float threshold, void* stream);
+
+/*
+ * Stage 2 — gather GEMV over the active rows of Wu, times the gate value.
+ * Consumes the list left by cats_gate / cats_compact; leaves h = gate * (Wu x) per list entry
+ * in the workspace for cats_down.  Optional inter_dense [B, I] (dtype) receives the same values
+ * scattered to their neuron positions (inactive positions are NOT written: clear it first).
+ * Replaces fuse_flag_gemv_local (fuse_gemv_cmp_cuda.cu:1507-1722, 2123-2156).
+ */
+int cats_up(const void* x, const void* Wu, void* ws, size_t ws_bytes, int B, int H, int I,
+            int dtype, void* inter_dense, void* stream);
+
+/*
+ * Stage 3 — down projection over the active rows of WdT [I, H] (split-K, fp32 accumulation).
+ * Consumes the list and h left by cats_up (or by cats_compact, whose values then act as h).
+ * Replaces atomic_gemv (fuse_gemv_cmp_cuda.cu:1724-1783, 2162-2194) and the Triton
+ * gather_transposed_gemv_flag_3d (flash_gemv/flash_gemv/kernels.py:256-462).
+ */
+int cats_down(const void* WdT, void* ws, size_t ws_bytes, int B, int H, int I, int dtype,
+              void* out, int out_mode, void* stream);
+
+/*
+ * Stages 2+3 in one launch: each CTA computes h for its share of the active list and
+ * immediately streams the matching WdT rows.  Optional fused decoder-layer tail (either NULL):
+ *   resid  [B, H] (dtype)  residual stream, updated in place: resid += mlp_out
+ *   x_next [B, H] (dtype)  RMS-normalised new residual: resid / sqrt(mean(resid^2) + eps),
+ *                          times norm_weight[H] (dtype) when that is not NULL
+ * (resid/x_next require out_mode == CATS_OUT_STORE; `out` may be NULL when resid is given.)
+ */
+int cats_updown(const void* x, const void* Wu, const void* WdT, void* ws, size_t ws_bytes,
+                int B, int H, int I, int dtype, void* out, int out_mode, void* resid,
+                void* x_next, const void* norm_weight, float eps, void* stream);
+
+/*
+ * The whole CATS MLP for decode: cats_gate followed by cats_updown with programmatic dependent
+ * launch between them.  Replaces flag_gemv_gemv_inner / _fp32 / _bf16
+ * (flash_gemv/flash_gemv/flash_gemv.py:36-43; fuse_gemv_cmp_cuda.cu:2330-2560), which take
+ * Wd [H, I]; here the caller passes the pre-packed WdT [I, H].
+ */
+int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, void* ws,
+             size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
+             int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
+             void* stream);
+
+/*
+ * A stack of L CATS MLP layers chained through the fused residual + RMS-norm tail, launched
+ * back to back without returning to the caller: layer l reads x_l, updates resid in place and
+ * writes x_{l+1}.  Pointer arrays live in HOST memory and hold device pointers.
+ *   x_io [B, H]: input of layer 0 on entry, RMS-normalised residual after layer L-1 on return.
+ * No reference counterpart as one call: it is the loop `for layer in model.layers: mlp(...)`
+ * of the decoder (experiments/models/sparse_silu/ugly_utils.py:1036-1057) for the MLP halves.
+ */
+int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const void* const* WdT,
+                   const float* thresholds, void* x_io, void* x_tmp, void* resid, void* ws,
+                   size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream);
+
+/*
+ * Dense down projection over Wd [H, I] (nn.Linear layout): out[b,h] = sum_i Wd[h,i] * inter[b,i].
+ * Reads all of Wd whatever the sparsity; exists for callers that cannot supply WdT.
+ * Replaces gemv_local_kernel (fuse_gemv_cmp_cuda.cu:1786-1960).
+ */
+int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int dtype, void* out,
+                    void* stream);
+
+/*
+ * The decoder-layer tail as a separate launch: resid[B,H] += y[B,H]; x_next = resid /
+ * sqrt(mean(resid^2) + eps) (times norm_weight[H] if given; x_next may be NULL).  For callers
+ * that must combine partial MLP outputs (tensor-parallel all-reduce) before the residual add;
+ * single-GPU callers get the same arithmetic fused into cats_updown / cats_mlp.  Restates the
+ * residual add + RMS norm around the MLP of the decoder layer
+ * (experiments/models/sparse_silu/ugly_utils.py:1036-1057).
+ */
+int cats_tail(const void* y, void* resid, void* x_next, const void* norm_weight, float eps, int B,
+              int H, int dtype, void* stream);
+
+/* Transpose a [rows, cols] matrix into [cols, rows] (packs Wd [H,I] into WdT [I,H]). */
+int cats_transpose(const void* src, void* dst, int rows, int cols, int dtype, void* stream);
+
+/*
+ * Read back, after synchronising `stream`, the number of active neurons (union over the batch)
+ * of the most recent stage-1/compact call on this workspace and the sticky device status word
+ * (0 = no device-side check failed).  The only entry point that blocks the host.  Serves the
+ * int return of fuse_gemv_cmp (fuse_gemv_cmp_cuda.cu:1962-1977).
+ */
+int cats_read_counters(const void* ws, int* n_active, int* device_status, void* stream);
+
+/*
+ * Copy the ordered active list of the most recent stage-1/compact call into caller buffers
+ * (device memory): idx_out int64[>= n_active], val_out (dtype)[>= n_active] for token 0.
+ * Serves fuse_gemv_cmp (flash_gemv/flash_gemv/flash_gemv.py:3-4), whose list is unordered in
+ * the reference; here it is ascending.
+ */
+int cats_export_list(const void* ws, size_t ws_bytes, int B, int H, int I, int dtype,
+                     int64_t* idx_out, void* val_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CATS_B200_H_ */
