@@ -21,6 +21,7 @@ SOURCES = ["cats_abi.cu"]
 HEADERS = [
     os.path.join(CSRC, "cats_common.cuh"),
     os.path.join(CSRC, "cats_kernels.cuh"),
+    os.path.join(CSRC, "cats_tma.cuh"),
     os.path.join(ROOT, "include", "cats_b200.h"),
 ]
 NVCC_FLAGS = [

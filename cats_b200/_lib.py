@@ -27,6 +27,7 @@ SIGNATURES = {
     "cats_status_string": (ctypes.c_char_p, [_c_int]),
     "cats_last_cuda_error": (ctypes.c_char_p, []),
     "cats_sm_count": (_c_int, []),
+    "cats_set_option": (_c_int, [ctypes.c_char_p, _c_int]),
     "cats_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int]),
     "cats_workspace_init": (_c_int, [_c_void_p, _c_size_t, _c_void_p]),
     "cats_gate": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int,

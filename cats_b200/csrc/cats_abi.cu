@@ -4,7 +4,9 @@
 
 #include <string.h>
 
-#include "cats_kernels.cuh"
+#include <stdlib.h>
+
+#include "cats_tma.cuh"
 
 namespace {
 
@@ -57,6 +59,8 @@ int cuda_status(cudaError_t e) {
   return CATS_ERR_CUDA;
 }
 
+int g_use_pdl = 1;  // cats_set_option("pdl", 0) launches without programmatic dependencies
+
 // Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while
 // its predecessor drains; every kernel here calls griddepcontrol.wait before touching data.
 template <typename... KArgs, typename... Args>
@@ -72,7 +76,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -161,8 +165,183 @@ cudaError_t run_rows_gemv(const void* xs, const void* W, int B, int K, int R, vo
                 K, R, (T*)out);
 }
 
+// ---- tuning knobs (cats_set_option) ------------------------------------------------------------
+struct Options {
+  int use_tma = 1;     // TMA-fed kernels where the shape allows (else the direct-load kernels)
+  int ring_kb = 200;   // shared-memory ring per TMA kernel
+};
+Options& options() {
+  static Options o = [] {
+    Options v;
+    if (const char* e = getenv("CATS_B200_TMA")) v.use_tma = atoi(e);
+    if (const char* e = getenv("CATS_B200_RING_KB")) v.ring_kb = atoi(e);
+    if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
+    return v;
+  }();
+  return o;
+}
+
+struct TmaPlan {
+  bool ok = false, xs = false;
+  int S = 0, grid = 0, sr = 1, nvt = 1, cap = 0, rmax = 0, cw = 1, pw = 1;
+  size_t smem = 0;
+};
+
+// Largest stage count <= smax (looking at most 3 below it) whose largest divisor <= 8 — the
+// number of consumer warps that can stride over the ring — is biggest.
+void pick_stages(int smax, int* S, int* cw) {
+  *S = 0;
+  *cw = 0;
+  for (int cand = smax; cand >= 2 && cand >= smax - 3; --cand) {
+    int d_best = 1;
+    for (int d = 1; d <= kConsumerWarps; ++d)
+      if (cand % d == 0) d_best = d;
+    if (d_best > *cw) {
+      *cw = d_best;
+      *S = cand;
+    }
+  }
+}
+
+TmaPlan plan_gate_tma(int B, int H, int I, int dtype) {
+  TmaPlan p;
+  const Options& o = options();
+  if (!o.use_tma || B > 4) return p;
+  const size_t row_bytes = (size_t)H * esize(dtype);
+  if (row_bytes % 16) return p;
+  const size_t xbytes = (size_t)B * row_bytes;
+  p.xs = xbytes <= 32 * 1024;
+  size_t budget = (size_t)o.ring_kb * 1024;
+  if (p.xs) budget = budget > xbytes + 32 * 1024 ? budget - xbytes : 32 * 1024;
+  p.sr = (row_bytes <= 8192) ? 2 : 1;
+  const size_t stage = p.sr * row_bytes;
+  int smax = (int)(budget / stage);
+  if (smax > 16) smax = 16;
+  if (smax < 2) return p;
+  pick_stages(smax, &p.S, &p.cw);
+  p.pw = (stage < 16 * 1024 && p.S % 2 == 0) ? 2 : 1;
+  p.grid = dev_info().sms;
+  if (p.grid > I) p.grid = I;
+  p.rmax = (I + p.grid - 1) / p.grid;
+  p.smem = align_up(p.S * stage + 16 * (size_t)p.S + 4 * (size_t)p.rmax * batch_tile(B), 16) +
+           (p.xs ? xbytes : 0);
+  p.ok = p.smem + 2048 <= (size_t)dev_info().max_smem_optin;
+  return p;
+}
+
+TmaPlan plan_updown_tma(int B, int H, int I, int dtype) {
+  TmaPlan p;
+  const Options& o = options();
+  if (!o.use_tma || B > 4) return p;
+  const size_t row_bytes = (size_t)H * esize(dtype);
+  if (row_bytes % 16) return p;
+  const int nvec = H / vecn(dtype);
+  const int need = (nvec + kConsumerThreads - 1) / kConsumerThreads;
+  p.nvt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+  if (need > 8) return p;
+  const size_t xbytes = (size_t)B * row_bytes;
+  p.xs = xbytes <= 32 * 1024;
+  size_t budget = (size_t)o.ring_kb * 1024;
+  if (p.xs) budget = budget > xbytes + 32 * 1024 ? budget - xbytes : 32 * 1024;
+  int smax = (int)(budget / row_bytes);
+  if (smax > 32) smax = 32;
+  if (smax < 2) return p;
+  pick_stages(smax, &p.S, &p.cw);
+  p.pw = (row_bytes < 16 * 1024 && p.S % 2 == 0) ? 2 : 1;
+  p.grid = dev_info().sms;
+  const int by_rows = (I + 7) / 8;
+  if (p.grid > by_rows) p.grid = by_rows;
+  p.cap = (I + p.grid - 1) / p.grid;
+  p.smem = align_up(p.S * row_bytes + 16 * (size_t)p.S +
+                        4 * (size_t)p.cap * (1 + batch_tile(B)), 16) +
+           (p.xs ? xbytes : 0);
+  p.ok = p.smem + 8192 <= (size_t)dev_info().max_smem_optin;
+  return p;
+}
+
+template <typename T, int BT, int SR, bool XS>
+cudaError_t run_gate_tma_v(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B,
+                           int H, int I, float thr, void* gate_dense, uint8_t* flag_dense,
+                           cudaStream_t st) {
+  return launch(k_gate_tma<T, BT, SR, XS>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
+                (const T*)x, (const T*)Wg, ws, B, H, I, thr, (T*)gate_dense, flag_dense, p.S,
+                p.cw, p.rmax);
+}
+
+template <typename T, int BT>
+cudaError_t run_gate_tma(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B, int H,
+                         int I, float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
+  if (p.sr == 2) {
+    if (p.xs) return run_gate_tma_v<T, BT, 2, true>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
+    return run_gate_tma_v<T, BT, 2, false>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
+  }
+  if (p.xs) return run_gate_tma_v<T, BT, 1, true>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
+  return run_gate_tma_v<T, BT, 1, false>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
+}
+
+template <typename T, int BT, int NVT>
+cudaError_t run_updown_tma_nvt(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
+                               WsPtrs ws, int B, int H, int I, void* out, int out_mode,
+                               void* resid, void* x_next, const void* norm_w, float eps,
+                               cudaStream_t st) {
+  if (p.xs)
+    return launch(k_updown_tma<T, BT, NVT, true>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
+                  (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
+                  (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
+  return launch(k_updown_tma<T, BT, NVT, false>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
+                (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
+                (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
+}
+
+template <typename T, int BT>
+cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
+                           WsPtrs ws, int B, int H, int I, void* out, int out_mode, void* resid,
+                           void* x_next, const void* norm_w, float eps, cudaStream_t st) {
+  switch (p.nvt) {
+    case 1: return run_updown_tma_nvt<T, BT, 1>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
+    case 2: return run_updown_tma_nvt<T, BT, 2>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
+    case 4: return run_updown_tma_nvt<T, BT, 4>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
+    default: return run_updown_tma_nvt<T, BT, 8>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
+  }
+}
+
+// B <= 4 only (the TMA kernels are instantiated for batch tiles 1, 2, 4)
+#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...)                                   \
+  do {                                                                           \
+    if ((dtype) == CATS_F32) {                                                   \
+      if (BT_ == 1) return FN<float, 1>(__VA_ARGS__);                            \
+      if (BT_ == 2) return FN<float, 2>(__VA_ARGS__);                            \
+      return FN<float, 4>(__VA_ARGS__);                                          \
+    }                                                                            \
+    if ((dtype) == CATS_F16) {                                                   \
+      if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__);                           \
+      if (BT_ == 2) return FN<__half, 2>(__VA_ARGS__);                           \
+      return FN<__half, 4>(__VA_ARGS__);                                         \
+    }                                                                            \
+    if (BT_ == 1) return FN<__nv_bfloat16, 1>(__VA_ARGS__);                      \
+    if (BT_ == 2) return FN<__nv_bfloat16, 2>(__VA_ARGS__);                      \
+    return FN<__nv_bfloat16, 4>(__VA_ARGS__);                                    \
+  } while (0)
+
+cudaError_t do_gate_tma(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B, int H,
+                        int I, int dtype, float thr, void* gate_dense, uint8_t* flag_dense,
+                        cudaStream_t st) {
+  CATS_DISPATCH_TMA(dtype, batch_tile(B), run_gate_tma, p, x, Wg, ws, B, H, I, thr, gate_dense,
+                    flag_dense, st);
+}
+
+cudaError_t do_updown_tma(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
+                          WsPtrs ws, int B, int H, int I, int dtype, void* out, int out_mode,
+                          void* resid, void* x_next, const void* norm_w, float eps,
+                          cudaStream_t st) {
+  CATS_DISPATCH_TMA(dtype, batch_tile(B), run_updown_tma, p, x, Wu, WdT, ws, B, H, I, out,
+                    out_mode, resid, x_next, norm_w, eps, st);
+}
+
 cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, int dtype,
                     float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
+  const TmaPlan p = plan_gate_tma(B, H, I, dtype);
+  if (p.ok) return do_gate_tma(p, x, Wg, ws, B, H, I, dtype, thr, gate_dense, flag_dense, st);
   CATS_DISPATCH(dtype, batch_tile(B), run_gate, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense,
                 st);
 }
@@ -170,6 +349,12 @@ cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int 
 cudaError_t do_updown(int mode, const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
                       int H, int I, int dtype, void* out, int out_mode, void* resid, void* x_next,
                       const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
+  if (mode == 3) {
+    const TmaPlan p = plan_updown_tma(B, H, I, dtype);
+    if (p.ok)
+      return do_updown_tma(p, x, Wu, WdT, ws, B, H, I, dtype, out, out_mode, resid, x_next, norm_w,
+                           eps, st);
+  }
   CATS_DISPATCH(dtype, batch_tile(B), run_updown, mode, x, Wu, WdT, ws, B, H, I, out, out_mode,
                 resid, x_next, norm_w, eps, inter_dense, st);
 }
@@ -208,6 +393,15 @@ const char* cats_status_string(int status) {
 const char* cats_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
 int cats_sm_count(void) { return dev_info().sms; }
+
+int cats_set_option(const char* name, int value) {
+  if (!name) return CATS_ERR_NULL;
+  if (!strcmp(name, "tma")) options().use_tma = value;
+  else if (!strcmp(name, "ring_kb")) options().ring_kb = value;
+  else if (!strcmp(name, "pdl")) g_use_pdl = value;
+  else return CATS_ERR_MODE;
+  return CATS_OK;
+}
 
 size_t cats_workspace_bytes(int B, int H, int I) {
   (void)B;

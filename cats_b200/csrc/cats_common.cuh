@@ -85,7 +85,31 @@ struct VecT<float> {
   }
   static __device__ __forceinline__ float to_f(float v) { return v; }
   static __device__ __forceinline__ float from_f(float v) { return v; }
+  // acc0 += a . x, acc1 += b . x over the 4 elements of the vectors
+  static __device__ __forceinline__ void fma2(const uint4& a, const uint4& b, const uint4& x,
+                                              float& acc0, float& acc1) {
+    float fa[4], fb[4], fx[4];
+    unpack(a, fa);
+    unpack(b, fb);
+    unpack(x, fx);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc0 = fmaf(fa[i], fx[i], acc0);
+      acc1 = fmaf(fb[i], fx[i], acc1);
+    }
+  }
 };
+
+// Blackwell mixed-precision FMA: d = a * b + c with 16-bit a, b and fp32 c, d.  The product of
+// two 16-bit floats is exact in fp32, so this equals fmaf(float(a), float(b), c) without the two
+// conversions.  One call handles a packed pair from each of two weight rows against one x pair.
+#define CATS_MIXED_FMA2(SUFFIX)                                                              \
+  asm("{\n\t.reg .b16 al, ah, bl, bh, xl, xh;\n\t"                                           \
+      "mov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\tmov.b32 {xl, xh}, %4;\n\t"          \
+      "fma.rn.f32." SUFFIX " %0, al, xl, %0;\n\tfma.rn.f32." SUFFIX " %1, bl, xl, %1;\n\t"   \
+      "fma.rn.f32." SUFFIX " %0, ah, xh, %0;\n\tfma.rn.f32." SUFFIX " %1, bh, xh, %1;\n\t}"  \
+      : "+f"(acc0), "+f"(acc1)                                                               \
+      : "r"(aw), "r"(bw), "r"(xw))
 
 template <>
 struct VecT<__half> {
@@ -101,6 +125,16 @@ struct VecT<__half> {
   }
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ void fma2(const uint4& a, const uint4& b, const uint4& x,
+                                              float& acc0, float& acc1) {
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w},
+                   xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t aw = av[i], bw = bv[i], xw = xv[i];
+      CATS_MIXED_FMA2("f16");
+    }
+  }
 };
 
 template <>
@@ -117,6 +151,16 @@ struct VecT<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) {
     return __float2bfloat16_rn(v);
+  }
+  static __device__ __forceinline__ void fma2(const uint4& a, const uint4& b, const uint4& x,
+                                              float& acc0, float& acc1) {
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w},
+                   xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t aw = av[i], bw = bv[i], xw = xv[i];
+      CATS_MIXED_FMA2("bf16");
+    }
   }
 };
 
@@ -171,22 +215,9 @@ __device__ __forceinline__ bool is_active(float v, float t) { return !(fabsf(v) 
 template <typename T, int BT>
 __device__ __forceinline__ void fma_vec2(const uint4& a, const uint4& b, const uint4* px, int nvec,
                                          int v, int B, float (&acc)[2][BT]) {
-  using V = VecT<T>;
-  constexpr int N = V::N;
-  float fa[N], fb[N];
-  V::unpack(a, fa);
-  V::unpack(b, fb);
 #pragma unroll
   for (int t = 0; t < BT; ++t) {
-    if (t < B) {
-      float fx[N];
-      V::unpack(__ldg(px + (size_t)t * nvec + v), fx);
-#pragma unroll
-      for (int i = 0; i < N; ++i) {
-        acc[0][t] = fmaf(fa[i], fx[i], acc[0][t]);
-        acc[1][t] = fmaf(fb[i], fx[i], acc[1][t]);
-      }
-    }
+    if (t < B) VecT<T>::fma2(a, b, __ldg(px + (size_t)t * nvec + v), acc[0][t], acc[1][t]);
   }
 }
 

@@ -94,16 +94,27 @@ k_gate(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, int 
 // Inclusive scan of the segment counts into shared memory; returns the total.
 // s_incl must hold kMaxSeg ints, s_part kWarps + 1 ints.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ int scan_segments(const int* __restrict__ seg_count, int nseg,
+__device__ __forceinline__ int scan_segments(const int* __restrict__ seg_count,
+                                             const int* __restrict__ nseg_ptr, int* nseg_out,
                                              int* s_incl, int* s_part) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int PER = kMaxSeg / kThreads;  // 4 consecutive entries per thread
+  // the counts are fetched before the segment count is known (one L2 round trip instead of
+  // two); entries past nseg are stale and masked below
   int loc[PER];
+  if (tid < kThreads) {
+    const int4 c4 = __ldcg(reinterpret_cast<const int4*>(seg_count) + tid);
+    loc[0] = c4.x; loc[1] = c4.y; loc[2] = c4.z; loc[3] = c4.w;
+  } else {
+    loc[0] = loc[1] = loc[2] = loc[3] = 0;
+  }
+  const int nseg = __ldcg(nseg_ptr);
+  *nseg_out = nseg;
   int sum = 0;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int s = tid * PER + i;
-    loc[i] = (s < nseg) ? __ldcg(seg_count + s) : 0;
+    if (s >= nseg) loc[i] = 0;
     sum += loc[i];
     loc[i] = sum;
   }
@@ -113,7 +124,7 @@ __device__ __forceinline__ int scan_segments(const int* __restrict__ seg_count, 
     int y = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += y;
   }
-  if (lane == 31) s_part[warp] = incl;
+  if (lane == 31 && warp < kWarps) s_part[warp] = incl;
   __syncthreads();
   if (warp == 0) {
     int w = (lane < kWarps) ? s_part[lane] : 0;
@@ -125,12 +136,11 @@ __device__ __forceinline__ int scan_segments(const int* __restrict__ seg_count, 
     if (lane < kWarps) s_part[lane] = w;  // inclusive over warps
   }
   __syncthreads();
-  const int warp_excl = (warp == 0) ? 0 : s_part[warp - 1];
-  const int thread_excl = warp_excl + incl - sum;
+  if (tid < kThreads) {
+    const int warp_excl = (warp == 0) ? 0 : s_part[warp - 1];
+    const int thread_excl = warp_excl + incl - sum;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int s = tid * PER + i;
-    if (s < kMaxSeg) s_incl[s] = thread_excl + loc[i];
+    for (int i = 0; i < PER; ++i) s_incl[tid * PER + i] = thread_excl + loc[i];
   }
   __syncthreads();
   return s_part[kWarps - 1];
@@ -156,40 +166,92 @@ template <typename T>
 __device__ void finalize_down(WsPtrs ws, int B, int H, T* __restrict__ out, int out_mode,
                               T* __restrict__ resid, T* __restrict__ x_next,
                               const T* __restrict__ norm_w, float eps, float* s_red) {
+  // Any block size that is a whole number of warps, up to 32 warps (s_red[32]).  Every thread
+  // first issues all of its accumulator / residual loads (one L2 round trip for the lot), then
+  // stores; the new residual stays in registers for the norm when a token's share per thread
+  // fits (KV groups of four elements), else it is read back.
   using V = VecT<T>;
+  constexpr int KV = 8;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthr = blockDim.x, nwarp = nthr >> 5;
+  const int ngrp = H >> 2;  // H is a multiple of 4
+  const bool in_regs = ngrp <= KV * nthr;
   for (int b = 0; b < B; ++b) {
     float ss = 0.f;
-    for (int hcol = tid; hcol < H; hcol += kThreads) {
-      const size_t e = (size_t)b * H + hcol;
-      const float v = __ldcg(ws.acc32 + e);
-      ws.acc32[e] = 0.f;
-      if (out_mode == 1) {
-        reinterpret_cast<float*>(out)[e] += v;
-      } else {
-        if (out) out[e] = V::from_f(v);
-        if (resid) {
-          const T r = V::from_f(V::to_f(resid[e]) + v);
-          resid[e] = r;
-          const float rf = V::to_f(r);
-          ss = fmaf(rf, rf, ss);
+    float keep[KV][4];
+    for (int g0 = 0; g0 < ngrp; g0 += KV * nthr) {
+      float4 a[KV];
+      float r[KV][4];
+#pragma unroll
+      for (int j = 0; j < KV; ++j) {
+        const int g = g0 + j * nthr + tid;
+        a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < ngrp) {
+          a[j] = __ldcg(reinterpret_cast<const float4*>(ws.acc32 + (size_t)b * H) + g);
+          if (resid && out_mode != 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[j][i] = V::to_f(resid[(size_t)b * H + 4 * g + i]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < KV; ++j) {
+        const int g = g0 + j * nthr + tid;
+        if (g < ngrp) {
+          const size_t e = (size_t)b * H + 4 * (size_t)g;
+          reinterpret_cast<float4*>(ws.acc32 + (size_t)b * H)[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float v[4] = {a[j].x, a[j].y, a[j].z, a[j].w};
+          if (out_mode == 1) {
+            float* o = reinterpret_cast<float*>(out) + e;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] += v[i];
+          } else {
+            if (out) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) out[e + i] = V::from_f(v[i]);
+            }
+            if (resid) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const T rn = V::from_f(r[j][i] + v[i]);
+                resid[e + i] = rn;
+                const float rf = V::to_f(rn);
+                keep[j][i] = rf;
+                ss = fmaf(rf, rf, ss);
+              }
+            }
+          }
         }
       }
     }
-    if (resid && x_next) {
+    if (resid && x_next && out_mode != 1) {
       ss = warp_sum(ss);
       __syncthreads();
       if (lane == 0) s_red[warp] = ss;
       __syncthreads();
       float tot = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) tot += s_red[w];
+      for (int w = 0; w < nwarp; ++w) tot += s_red[w];
       const float rs = rsqrtf(tot / (float)H + eps);
-      for (int hcol = tid; hcol < H; hcol += kThreads) {
-        const size_t e = (size_t)b * H + hcol;
-        T y = V::from_f(V::to_f(resid[e]) * rs);
-        if (norm_w) y = V::from_f(V::to_f(norm_w[hcol]) * V::to_f(y));
-        x_next[e] = y;
+      if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < KV; ++j) {
+          const int g = j * nthr + tid;
+          if (g < ngrp) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              T y = V::from_f(keep[j][i] * rs);
+              if (norm_w) y = V::from_f(V::to_f(norm_w[4 * g + i]) * V::to_f(y));
+              x_next[(size_t)b * H + 4 * g + i] = y;
+            }
+          }
+        }
+      } else {
+        for (int hcol = tid; hcol < H; hcol += nthr) {
+          const size_t e = (size_t)b * H + hcol;
+          T y = V::from_f(V::to_f(resid[e]) * rs);
+          if (norm_w) y = V::from_f(V::to_f(norm_w[hcol]) * V::to_f(y));
+          x_next[e] = y;
+        }
       }
     }
   }
@@ -218,7 +280,7 @@ k_updown(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restrict_
   float* s_h = reinterpret_cast<float*>(s_dyn + cap + kRU);  // [(cap + kRU) * BT]
   __shared__ int s_incl[kUp ? kMaxSeg : 1];
   __shared__ int s_part[kWarps + 1];
-  __shared__ float s_red[kWarps];
+  __shared__ float s_red[32];
   __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -230,8 +292,7 @@ k_updown(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restrict_
 
   int n, nseg = 1;
   if (kUp) {
-    nseg = __ldcg(ws.hdr + HDR_NSEG);
-    n = scan_segments(ws.seg_count, nseg, s_incl, s_part);
+    n = scan_segments(ws.seg_count, ws.hdr + HDR_NSEG, &nseg, s_incl, s_part);
     if (c == 0 && tid == 0) ws.hdr[HDR_NACTIVE] = n;
   } else {
     n = __ldcg(ws.hdr + HDR_NACTIVE);
@@ -442,8 +503,8 @@ k_export(WsPtrs ws, int B, int I, long long* __restrict__ idx_out, T* __restrict
   __shared__ int s_incl[kMaxSeg];
   __shared__ int s_part[kWarps + 1];
   pdl_wait();
-  const int nseg = __ldcg(ws.hdr + HDR_NSEG);
-  const int n = scan_segments(ws.seg_count, nseg, s_incl, s_part);
+  int nseg;
+  const int n = scan_segments(ws.seg_count, ws.hdr + HDR_NSEG, &nseg, s_incl, s_part);
   if (blockIdx.x == 0 && threadIdx.x == 0) ws.hdr[HDR_NACTIVE] = n;
   for (int p = blockIdx.x * kThreads + threadIdx.x; p < n; p += gridDim.x * kThreads) {
     const int q = locate(s_incl, nseg, I, p);

@@ -64,6 +64,16 @@ const char* cats_last_cuda_error(void);
 int cats_sm_count(void);
 
 /*
+ * Tuning knob, process-wide.  "tma" (0/1): use the TMA-fed kernels where the shape allows
+ * (default 1; 0 forces the direct-load kernels).  "ring_kb": shared-memory ring per TMA kernel in
+ * KiB (default 200).  "pdl" (0/1): launch with programmatic dependent launch (default 1).  The
+ * same values are read once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB and
+ * CATS_B200_PDL.  No reference
+ * counterpart.
+ */
+int cats_set_option(const char* name, int value);
+
+/*
  * Workspace.  One workspace serves every call with batch <= B, hidden <= H, intermediate <= I
  * made in stream order on one stream; it holds the compacted active-neuron list, the per-neuron
  * gate values, fp32 split-K accumulators and a self-resetting completion ticket.  It has to be
