@@ -22,6 +22,7 @@ HEADERS = [
     os.path.join(CSRC, "cats_common.cuh"),
     os.path.join(CSRC, "cats_kernels.cuh"),
     os.path.join(CSRC, "cats_tma.cuh"),
+    os.path.join(CSRC, "cats_mega.cuh"),
     os.path.join(ROOT, "include", "cats_b200.h"),
 ]
 NVCC_FLAGS = [

@@ -6,7 +6,7 @@
 
 #include <stdlib.h>
 
-#include "cats_tma.cuh"
+#include "cats_mega.cuh"
 
 namespace {
 
@@ -96,12 +96,16 @@ int batch_tile(int B) { return B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : B <= 8 ? 8
     case 8: return FN<T, 8>(__VA_ARGS__);         \
     default: return FN<T, 16>(__VA_ARGS__);       \
   }
+#ifdef CATS_DEV_HALF_ONLY
+#define CATS_DISPATCH(dtype, BT_, FN, ...) return FN<__half, 1>(__VA_ARGS__)
+#else
 #define CATS_DISPATCH(dtype, BT_, FN, ...)                                     \
   do {                                                                         \
     if ((dtype) == CATS_F32) { CATS_DISPATCH_BT(float, BT_, FN, __VA_ARGS__) } \
     if ((dtype) == CATS_F16) { CATS_DISPATCH_BT(__half, BT_, FN, __VA_ARGS__) } \
     CATS_DISPATCH_BT(__nv_bfloat16, BT_, FN, __VA_ARGS__)                      \
   } while (0)
+#endif
 
 // ---- grid sizing --------------------------------------------------------------------------
 int gate_segments(int I) {
@@ -169,6 +173,7 @@ cudaError_t run_rows_gemv(const void* xs, const void* W, int B, int K, int R, vo
 struct Options {
   int use_tma = 1;     // TMA-fed kernels where the shape allows (else the direct-load kernels)
   int ring_kb = 200;   // shared-memory ring per TMA kernel
+  int use_mega = 1;    // persistent cooperative kernel for cats_mlp / cats_mlp_stack
 };
 Options& options() {
   static Options o = [] {
@@ -176,6 +181,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_TMA")) v.use_tma = atoi(e);
     if (const char* e = getenv("CATS_B200_RING_KB")) v.ring_kb = atoi(e);
     if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
+    if (const char* e = getenv("CATS_B200_MEGA")) v.use_mega = atoi(e);
     return v;
   }();
   return o;
@@ -305,7 +311,95 @@ cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, cons
   }
 }
 
+// ---- persistent kernel ------------------------------------------------------------------------
+struct MegaPlan {
+  bool ok = false;
+  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0;
+  size_t smem = 0;
+};
+
+MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
+  MegaPlan p;
+  const Options& o = options();
+  if (!o.use_mega || !o.use_tma || B > 4 || L < 1 || L > kMegaMaxLayers) return p;
+  if (L > 1 && !has_resid) return p;
+  const size_t row_bytes = (size_t)H * esize(dtype);
+  if (row_bytes % 16) return p;
+  const int nvec = H / vecn(dtype);
+  const int need = (nvec + kConsumerThreads - 1) / kConsumerThreads;
+  if (need > 8) return p;
+  p.nvt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+  p.grid = dev_info().sms;
+  if (p.grid > kMegaMaxGrid) p.grid = kMegaMaxGrid;
+  if (p.grid > I / 2) p.grid = I / 2;
+  if (p.grid < 1) return p;
+  const int half_rows = (I + 1) / 2;
+  p.rmax = (half_rows + p.grid - 1) / p.grid + 1;
+  p.cap = p.rmax;
+  const int bt = batch_tile(B);
+  const size_t fixed = 16 + (size_t)B * row_bytes * (has_resid ? 2 : 1) +
+                       2 * sizeof(float) * (size_t)p.rmax * bt + 2 * sizeof(int) * (size_t)p.cap +
+                       2 * sizeof(float) * (size_t)p.cap * bt;
+  const size_t limit = (size_t)dev_info().max_smem_optin;
+  const size_t statics = 2048;  // static shared memory of the kernel + slack
+  if (limit < fixed + statics + 2 * row_bytes + 1024) return p;
+  int smax = (int)((limit - fixed - statics - 1024) / (row_bytes + 16));
+  if (smax > 48) smax = 48;
+  // even stage count (two producers), as many dot-owner warps (a divisor <= 8) as possible
+  for (int cand = smax; cand >= 2 && cand >= smax - 5; --cand) {
+    if (cand & 1) continue;
+    int cw = 1;
+    for (int d = 1; d <= kConsumerWarps; ++d)
+      if (cand % d == 0) cw = d;
+    if (cw > p.cw || p.S == 0) {
+      if (p.S == 0 || cw > p.cw) {
+        p.cw = cw;
+        p.S = cand;
+      }
+    }
+  }
+  if (p.S < 2) return p;
+  p.smem = align_up((size_t)p.S * row_bytes + 8 * (size_t)(2 * p.S + 6), 16) + fixed;
+  p.ok = p.smem + statics <= limit;
+  return p;
+}
+
+template <typename T, int BT, int NVT>
+cudaError_t launch_mega(const MegaPlan& p, const MegaParams& P, const MegaArgs& A, WsPtrs ws,
+                        cudaStream_t st) {
+  auto kernel = k_cats_mega<T, BT, NVT>;
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(p.grid);
+  cfg.blockDim = dim3(kMegaThreads);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // CTAs wait for one another: must be co-resident
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, P, A, ws);
+}
+
+template <typename T, int BT>
+cudaError_t run_mega(const MegaPlan& p, const MegaParams& P, const MegaArgs& A, WsPtrs ws,
+                     cudaStream_t st) {
+  switch (p.nvt) {
+    case 1: return launch_mega<T, BT, 1>(p, P, A, ws, st);
+    case 2: return launch_mega<T, BT, 2>(p, P, A, ws, st);
+    case 4: return launch_mega<T, BT, 4>(p, P, A, ws, st);
+    default: return launch_mega<T, BT, 8>(p, P, A, ws, st);
+  }
+}
+
 // B <= 4 only (the TMA kernels are instantiated for batch tiles 1, 2, 4)
+#ifdef CATS_DEV_HALF_ONLY  // development builds: one instantiation, quick to compile
+#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...) return FN<__half, 1>(__VA_ARGS__)
+#else
 #define CATS_DISPATCH_TMA(dtype, BT_, FN, ...)                                   \
   do {                                                                           \
     if ((dtype) == CATS_F32) {                                                   \
@@ -322,6 +416,18 @@ cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, cons
     if (BT_ == 2) return FN<__nv_bfloat16, 2>(__VA_ARGS__);                      \
     return FN<__nv_bfloat16, 4>(__VA_ARGS__);                                    \
   } while (0)
+#endif
+
+cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs ws, int dtype,
+                    cudaStream_t st) {
+  A.S = p.S;
+  A.cw = p.cw;
+  A.npw = (p.S % kMegaProducers == 0) ? kMegaProducers : 2;
+  A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
+  A.cap = p.cap;
+  A.rmax = p.rmax;
+  CATS_DISPATCH_TMA(dtype, batch_tile(A.B), run_mega, p, P, A, ws, st);
+}
 
 cudaError_t do_gate_tma(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B, int H,
                         int I, int dtype, float thr, void* gate_dense, uint8_t* flag_dense,
@@ -399,6 +505,7 @@ int cats_set_option(const char* name, int value) {
   if (!strcmp(name, "tma")) options().use_tma = value;
   else if (!strcmp(name, "ring_kb")) options().ring_kb = value;
   else if (!strcmp(name, "pdl")) g_use_pdl = value;
+  else if (!strcmp(name, "mega")) options().use_mega = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }
@@ -500,6 +607,22 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
   WsPtrs p;
   if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_mode == CATS_OUT_STORE) {
+    const MegaPlan mp = plan_mega(1, B, H, I, dtype, resid != nullptr);
+    if (mp.ok) {
+      MegaParams P;
+      P.wg[0] = Wg;
+      P.wu[0] = Wu;
+      P.wdt[0] = WdT;
+      P.nw[0] = norm_weight;
+      P.thr[0] = threshold;
+      MegaArgs A;
+      memset(&A, 0, sizeof(A));
+      A.L = 1; A.B = B; A.H = H; A.I = I; A.eps = eps;
+      A.x_in = x; A.x_out = x_next; A.resid = resid; A.out_last = out;
+      return cuda_status(do_mega(mp, P, A, p, dtype, st));
+    }
+  }
   cudaError_t e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, out_mode, resid, x_next,
@@ -521,6 +644,22 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
   WsPtrs p;
   if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const MegaPlan mp = plan_mega(L, B, H, I, dtype, true);
+  if (mp.ok) {
+    MegaParams P;
+    for (int l = 0; l < L; ++l) {
+      P.wg[l] = Wg[l];
+      P.wu[l] = Wu[l];
+      P.wdt[l] = WdT[l];
+      P.nw[l] = nullptr;
+      P.thr[l] = thresholds[l];
+    }
+    MegaArgs A;
+    memset(&A, 0, sizeof(A));
+    A.L = L; A.B = B; A.H = H; A.I = I; A.eps = eps;
+    A.x_in = x_io; A.x_out = x_io; A.resid = resid; A.out_last = nullptr;
+    return cuda_status(do_mega(mp, P, A, p, dtype, st));
+  }
   void* cur = x_io;
   void* nxt = x_tmp;
   for (int l = 0; l < L; ++l) {
@@ -596,9 +735,9 @@ int cats_read_counters(const void* ws, int* n_active, int* device_status, void* 
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return cuda_status(e);
   int nseg = host[HDR_NSEG];
-  if (nseg < 0) nseg = 0;
   if (nseg > kMaxSeg) nseg = kMaxSeg;
   long long n = 0;
+  if (nseg < 0) n = host[HDR_NACTIVE];  // left by the persistent kernel (last layer's total)
   for (int c = 0; c < nseg; ++c) n += host[kHdrInts + c];
   if (n_active) *n_active = (int)n;
   if (device_status) *device_status = host[HDR_STATUS];

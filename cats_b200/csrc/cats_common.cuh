@@ -25,7 +25,7 @@ enum { HDR_NACTIVE = 0, HDR_TICKET = 1, HDR_STATUS = 2, HDR_NSEG = 3 };
 struct WsPtrs {
   int* hdr;          // [kHdrInts]
   int* seg_count;    // [kMaxSeg]   active neurons found by stage-1 CTA c
-  float* acc32;      // [kMaxB * H] split-K accumulators, zero between calls
+  float* acc32;      // [2][kMaxB * H] split-K accumulators (two buffers), zero between calls
   int* seg_idx;      // [I]         segment c's ordered neuron list starts at row0(c)
   float* seg_gate;   // [I * B]     gate value per list entry and token (0 = token inactive)
   int* flat_idx;     // [I]         globally ordered list (written by stage 2 / compact)
@@ -46,7 +46,7 @@ __host__ __device__ inline size_t ws_layout(void* base, int H, int I, WsPtrs* p)
   };
   size_t o_hdr = take(sizeof(int) * kHdrInts);
   size_t o_cnt = take(sizeof(int) * kMaxSeg);
-  size_t o_acc = take(sizeof(float) * (size_t)kMaxB * H);
+  size_t o_acc = take(sizeof(float) * 2 * (size_t)kMaxB * H);
   size_t o_sidx = take(sizeof(int) * (size_t)I);
   size_t o_sgate = take(sizeof(float) * (size_t)I * kMaxB);
   size_t o_fidx = take(sizeof(int) * (size_t)I);
@@ -98,6 +98,24 @@ struct VecT<float> {
       acc1 = fmaf(fb[i], fx[i], acc1);
     }
   }
+  // acc += a . x
+  static __device__ __forceinline__ void fma1(const uint4& a, const uint4& x, float& acc) {
+    float fa[4], fx[4];
+    unpack(a, fa);
+    unpack(x, fx);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc = fmaf(fa[i], fx[i], acc);
+  }
+  // scalar prepared for axpy (see the 16-bit specialisations)
+  typedef float Scalar;
+  static __device__ __forceinline__ Scalar prep(float h) { return h; }
+  // acc[i] += h * w[i]
+  static __device__ __forceinline__ void axpy(Scalar h, const uint4& w, float* acc) {
+    float fw[4];
+    unpack(w, fw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = fmaf(h, fw[i], acc[i]);
+  }
 };
 
 // Blackwell mixed-precision FMA: d = a * b + c with 16-bit a, b and fp32 c, d.  The product of
@@ -110,6 +128,12 @@ struct VecT<float> {
       "fma.rn.f32." SUFFIX " %0, ah, xh, %0;\n\tfma.rn.f32." SUFFIX " %1, bh, xh, %1;\n\t}"  \
       : "+f"(acc0), "+f"(acc1)                                                               \
       : "r"(aw), "r"(bw), "r"(xw))
+#define CATS_MIXED_FMA1(SUFFIX)                                                              \
+  asm("{\n\t.reg .b16 al, ah, xl, xh;\n\t"                                                   \
+      "mov.b32 {al, ah}, %1;\n\tmov.b32 {xl, xh}, %2;\n\t"                                    \
+      "fma.rn.f32." SUFFIX " %0, al, xl, %0;\n\tfma.rn.f32." SUFFIX " %0, ah, xh, %0;\n\t}"  \
+      : "+f"(acc)                                                                            \
+      : "r"(aw), "r"(xw))
 
 template <>
 struct VecT<__half> {
@@ -133,6 +157,35 @@ struct VecT<__half> {
     for (int i = 0; i < 4; ++i) {
       const uint32_t aw = av[i], bw = bv[i], xw = xv[i];
       CATS_MIXED_FMA2("f16");
+    }
+  }
+  static __device__ __forceinline__ void fma1(const uint4& a, const uint4& x, float& acc) {
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t aw = av[i], xw = xv[i];
+      CATS_MIXED_FMA1("f16");
+    }
+  }
+  // axpy without converting the weights: the fp32 scalar h is split into two halves,
+  // h ~= hi + lo (22 significant bits; exact to ~2^-22 relative for |h| >= 2^-3 and to 2^-25
+  // absolute below), and each weight takes two mixed-precision FMAs.  The conversion
+  // instruction it replaces runs at a fraction of the FMA rate and was the bottleneck.
+  typedef uint32_t Scalar;  // {hi, lo} packed
+  static __device__ __forceinline__ Scalar prep(float h) {
+    const __half hi = __float2half_rn(h);
+    const __half lo = __float2half_rn(h - __half2float(hi));
+    return (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+  }
+  static __device__ __forceinline__ void axpy(Scalar h, const uint4& w, float* acc) {
+    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      asm("{\n\t.reg .b16 wl, wh, hi, lo;\n\tmov.b32 {wl, wh}, %2;\n\tmov.b32 {hi, lo}, %3;\n\t"
+          "fma.rn.f32.f16 %0, wl, hi, %0;\n\tfma.rn.f32.f16 %0, wl, lo, %0;\n\t"
+          "fma.rn.f32.f16 %1, wh, hi, %1;\n\tfma.rn.f32.f16 %1, wh, lo, %1;\n\t}"
+          : "+f"(acc[2 * i]), "+f"(acc[2 * i + 1])
+          : "r"(wv[i]), "r"(h));
     }
   }
 };
@@ -161,6 +214,23 @@ struct VecT<__nv_bfloat16> {
       const uint32_t aw = av[i], bw = bv[i], xw = xv[i];
       CATS_MIXED_FMA2("bf16");
     }
+  }
+  static __device__ __forceinline__ void fma1(const uint4& a, const uint4& x, float& acc) {
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t aw = av[i], xw = xv[i];
+      CATS_MIXED_FMA1("bf16");
+    }
+  }
+  // bf16 -> fp32 is a shift / mask on the integer pipe: plain fp32 FMAs, exact
+  typedef float Scalar;
+  static __device__ __forceinline__ Scalar prep(float h) { return h; }
+  static __device__ __forceinline__ void axpy(Scalar h, const uint4& w, float* acc) {
+    float fw[8];
+    unpack(w, fw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(h, fw[i], acc[i]);
   }
 };
 

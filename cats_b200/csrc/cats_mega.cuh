@@ -1,0 +1,616 @@
+// Persistent CATS MLP kernel (sm_100a): every layer of a stack in ONE cooperative launch.
+//
+// Why.  A CATS layer moves ~235 MB (Mistral-7B shape, fp16, 50 % sparsity), about 35 us of HBM
+// time on a B200.  Split into a stage-1 launch and a stage-2/3 launch, every launch pays its own
+// ramp (first copies in flight), tail (slowest CTA, epilogue by one CTA) and hand-off; measured,
+// that is ~20 us per layer of HBM idling.  Here one CTA per SM stays resident for the whole
+// stack and keeps one stream of weight rows flowing through a shared-memory ring:
+//
+//   per layer:   G(0) G(1) U(0) D(0) U(1) D(1)        (G gate rows, U up rows, D down rows)
+//
+// The layer's neurons are split into two halves.  G(h) are the gate rows of this CTA's segment
+// of half h; after them the CTA publishes the segment's active list and arrives at a grid
+// barrier.  U(h)/D(h) are this CTA's balanced share of the active neurons of half h over ALL
+// CTAs, known once that barrier has completed.  Because G(1) is streamed between G(0) and U(0),
+// and U(0)/D(0) between G(1) and U(1), the barrier + scan latency of each half is covered by the
+// other half's rows: the producers normally never wait for a list.  The residual add and RMS
+// norm between layers are computed by every CTA for itself from the fp32 accumulators (no
+// "last CTA" epilogue), and the next layer's gate rows are already streaming while that happens.
+//
+// Roles in a CTA (416 threads): warps 0-7 consumers; warps 8-11 producers (one elected thread
+// each issues cp.async.bulk row copies, global -> this CTA's shared memory, never multicast; one
+// thread manages a copy roughly every 240 ns, a quarter of what an SM's HBM share needs at 8 KB
+// rows, hence four); warp 12 control (compacts and publishes the segment's active list, waits
+// for the grid barriers, scans the segment counts, fills the CTA's work list).
+//
+// Waits.  CTAs wait for one another at grid barriers, so the launch is cooperative (all CTAs
+// co-resident or the launch fails).  Every wait (mbarrier or grid barrier) is bounded (~1 s):
+// on a time-out the CTA sets an abort flag in shared memory and the status word of the
+// workspace, stops issuing copies, lets copies in flight land and leaves; the other CTAs then
+// run into their own limits and leave as well.
+#pragma once
+
+#include "cats_tma.cuh"
+
+namespace cats {
+
+constexpr int kMegaMaxLayers = 112;
+constexpr int kMegaMaxGrid = 256;
+constexpr int kMegaProducers = 4;  // issuing threads (one per warp); the host uses 2 when 4 does not divide S
+constexpr int kMegaWarps = kConsumerWarps + kMegaProducers + 1;
+constexpr int kMegaThreads = kMegaWarps * 32;
+constexpr int kSegHalfStride = kMaxSeg / 2;  // seg_count slots of half 1 start here
+
+enum { STATUS_WAIT_TIMEOUT_MEGA = 3 };
+enum { HDR_GBAR = 8, HDR_GBAR_BASE = 9 };
+
+struct MegaParams {
+  const void* wg[kMegaMaxLayers];
+  const void* wu[kMegaMaxLayers];
+  const void* wdt[kMegaMaxLayers];
+  const void* nw[kMegaMaxLayers];  // optional RMS-norm weight applied to the layer's x_next
+  float thr[kMegaMaxLayers];
+};
+
+struct MegaArgs {
+  int L, B, H, I;
+  int S, cw, cap, rmax;  // ring stages, dot-owner warps (divides S), list capacity, rows/segment
+  int npw;               // producer threads in use (divides S)
+  unsigned s_magic;      // floor(2^32 / S) + 1: item -> (ring cycle, slot) without a division
+  float eps;
+  const void* x_in;  // [B,H] input of layer 0
+  void* x_out;       // [B,H] normalised residual after the last layer (needs resid), or null
+  void* resid;       // [B,H] residual stream in/out, or null (then L must be 1)
+  void* out_last;    // [B,H] raw MLP output of the last layer, or null
+};
+
+// Rows [lo, hi) of half h out of I.
+__host__ __device__ inline int half_row0(int h, int I) { return (int)(((long long)I * h) / 2); }
+
+// ---- grid barrier on a monotonic counter ------------------------------------------------------
+__device__ __forceinline__ void grid_arrive(unsigned* ctr) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded spin until the counter has reached `target` (wrap-safe compare).
+__device__ __forceinline__ bool grid_wait(const unsigned* ctr, unsigned target,
+                                          volatile int* abort) {
+  if ((int)(ld_acquire_gpu(ctr) - target) >= 0) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if ((int)(ld_acquire_gpu(ctr) - target) >= 0) return true;
+      __nanosleep(40);
+    }
+    if (*abort) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort = 1;
+      return false;
+    }
+  }
+}
+
+template <typename T, int BT, int NVT>
+__global__ void __launch_bounds__(kMegaThreads, 1)
+k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
+  using V = VecT<T>;
+  constexpr int N = V::N;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_abort;
+  __shared__ float s_red[32];
+  __shared__ int s_cnt[2];
+  __shared__ int s_pref[kMegaMaxGrid];
+
+  const int L = A.L, B = A.B, H = A.H, I = A.I, S = A.S, cw = A.cw;
+  const uint32_t row_bytes = (uint32_t)H * sizeof(T);
+  const int nvec = H / N;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = gridDim.x, c = blockIdx.x;
+  const bool has_resid = A.resid != nullptr;
+  const unsigned s_magic = A.s_magic;
+  // ring cycle (k / S) and slot (k % S) of item k; exact for k < 2^32 / S
+  auto cyc_of = [&](int kk) { return (int)__umulhi((unsigned)kk, s_magic); };
+  auto slot_of = [&](int kk) { return kk - cyc_of(kk) * S; };
+
+  // ---- shared memory carve-up -----------------------------------------------------------------
+  unsigned char* ring = smem;
+  size_t off = (size_t)S * row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off);
+  off += 8 * (size_t)(2 * S + 6);
+  off = align_up(off, 16);
+  T* xs = reinterpret_cast<T*>(smem + off);
+  off += (size_t)B * row_bytes;
+  T* rs = reinterpret_cast<T*>(smem + off);
+  off += has_resid ? (size_t)B * row_bytes : 0;
+  float* s_val = reinterpret_cast<float*>(smem + off);  // [2][rmax * BT]
+  off += 2 * sizeof(float) * (size_t)A.rmax * BT;
+  int* s_idx = reinterpret_cast<int*>(smem + off);  // [2][cap]
+  off += 2 * sizeof(int) * (size_t)A.cap;
+  float* s_hg = reinterpret_cast<float*>(smem + off);  // [2][cap * BT]
+
+  const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(bars), empty_u = full_u + 8u * S;
+  const uint32_t lready_u = empty_u + 8u * S, lfree_u = lready_u + 16u, gdone_u = lfree_u + 16u;
+
+  unsigned* gbar = reinterpret_cast<unsigned*>(ws.hdr + HDR_GBAR);
+  const unsigned gbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_GBAR_BASE));
+  auto gtarget = [&](int idx) { return gbase + (unsigned)(idx + 1) * (unsigned)G; };
+  // barrier indices: 3*l + h after the gate rows of half h, 3*l + 2 after the layer's down rows,
+  // 3*L at the very end
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_u + 8u * s, 1);
+      mbar_init(empty_u + 8u * s, kConsumerWarps);
+    }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(lready_u + 8u * h, 1);
+      mbar_init(lfree_u + 8u * h, kConsumerWarps);
+      mbar_init(gdone_u + 8u * h, kConsumerWarps);
+    }
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  stage_x<T>(reinterpret_cast<const T*>(A.x_in), xs, B, H);
+  if (has_resid) stage_x<T>(reinterpret_cast<const T*>(A.resid), rs, B, H);
+  __syncthreads();
+
+  // this CTA's gate segment of half h
+  auto seg_lo = [&](int h) {
+    const int lo = half_row0(h, I), hi = half_row0(h + 1, I);
+    return lo + seg_row0(c, G, hi - lo);
+  };
+  auto seg_hi = [&](int h) {
+    const int lo = half_row0(h, I), hi = half_row0(h + 1, I);
+    return lo + seg_row0(c + 1, G, hi - lo);
+  };
+
+  if (warp >= kConsumerWarps && warp < kConsumerWarps + kMegaProducers) {
+    // =========================================================================== producers
+    const int npw = A.npw;
+    if (lane == 0 && warp - kConsumerWarps < npw) {
+      const int p = warp - kConsumerWarps;
+      bool ok = true;
+      int k = 0;
+      auto issue = [&](int kk, const T* src) {
+        const int cy = cyc_of(kk), s = kk - cy * S;
+        if (kk >= S && !mbar_wait(empty_u + 8u * s, (cy - 1) & 1, &s_abort)) {
+          ok = false;
+          return;
+        }
+        mbar_expect_tx(full_u + 8u * s, row_bytes);
+        tma_load_1d(ring_u + s * row_bytes, src, row_bytes, full_u + 8u * s);
+      };
+      for (int l = 0; l < L && ok; ++l) {
+        const bool tl = (l == L / 2) && p == 0;
+        CATS_STAMP(1, 0, tl);
+        const T* Wg = reinterpret_cast<const T*>(P.wg[l]);
+        const T* Wu = reinterpret_cast<const T*>(P.wu[l]);
+        const T* Wd = reinterpret_cast<const T*>(P.wdt[l]);
+        for (int h = 0; h < 2 && ok; ++h) {
+          const int r0 = seg_lo(h), R = seg_hi(h) - r0;
+          for (int j = 0; j < R && ok; ++j)
+            if ((k + j) % npw == p) issue(k + j, Wg + (size_t)(r0 + j) * H);
+          k += R;
+          CATS_STAMP(1, 1 + h, tl);
+        }
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!mbar_wait(lready_u + 8u * h, l & 1, &s_abort)) {
+            ok = false;
+            break;
+          }
+          CATS_STAMP(1, 3 + 2 * h, tl);
+          const int cnt = s_cnt[h];
+          const int* idx = s_idx + h * A.cap;
+          for (int j = 0; j < cnt && ok; ++j)
+            if ((k + j) % npw == p) issue(k + j, Wu + (size_t)idx[j] * H);
+          k += cnt;
+          for (int j = 0; j < cnt && ok; ++j)
+            if ((k + j) % npw == p) {
+#ifdef CATS_PHASE_TIMING
+              if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[2][j] = cats_now();
+#endif
+              issue(k + j, Wd + (size_t)idx[j] * H);
+#ifdef CATS_PHASE_TIMING
+              if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[3][j] = cats_now();
+#endif
+            }
+          k += cnt;
+          CATS_STAMP(1, 4 + 2 * h, tl);
+        }
+      }
+    }
+  } else if (warp == kConsumerWarps + kMegaProducers) {
+    // =========================================================================== control
+    // Warp-uniform control flow on purpose: every lane polls in the waits and nothing is done
+    // under `if (lane == 0)` except single stores.  (With lane-0-only waits and early exits the
+    // warp ran its shuffles diverged, which made this section ~40x slower.)
+    bool ok = true;
+    for (int l = 0; l < L; ++l) {
+      const float thr = P.thr[l];
+      for (int h = 0; h < 2; ++h) {
+        const bool tl = (l == L / 2) && lane == 0;
+        // ---- this CTA's gate values of half h are in: ballot / popc compaction, publish, arrive
+        if (ok) ok = mbar_wait(gdone_u + 8u * h, l & 1, &s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          const int r0 = seg_lo(h), R = seg_hi(h) - r0;
+          const float* sv = s_val + (size_t)h * A.rmax * BT;
+          int base = 0;
+          for (int g0 = 0; g0 < R; g0 += 32) {
+            const int lr = g0 + lane;
+            float v[BT];
+            bool any = false;
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              v[t] = 0.f;
+              if (lr < R && t < B) {
+                const float sval = sv[lr * BT + t];
+                const bool a = is_active(sval, thr);
+                v[t] = a ? sval : 0.f;
+                any |= a;
+              }
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, any);
+            if (any) {
+              const int pos = r0 + base + __popc(m & ((1u << lane) - 1u));
+              ws.seg_idx[pos] = r0 + lr;
+#pragma unroll
+              for (int t = 0; t < BT; ++t)
+                if (t < B) ws.seg_gate[(size_t)pos * B + t] = v[t];
+            }
+            base += __popc(m);
+          }
+          if (lane == 0) ws.seg_count[h * kSegHalfStride + c] = base;
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) grid_arrive(gbar);
+        }
+        CATS_STAMP(1, 8 + 3 * h, tl);
+        // ---- all CTAs have published half h: scan the counts, take this CTA's balanced share
+        if (ok) ok = grid_wait(gbar, gtarget(3 * l + h), &s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        CATS_STAMP(1, 9 + 3 * h, tl);
+        const int* cntp = ws.seg_count + h * kSegHalfStride;
+        int cv[kMegaMaxGrid / 32];
+#pragma unroll
+        for (int q = 0; q < kMegaMaxGrid / 32; ++q) {  // all loads first: one L2 round trip
+          const int i = q * 32 + lane;
+          cv[q] = (ok && i < G) ? __ldcg(cntp + i) : 0;
+        }
+        if (ok && h == 0 && l >= 1) {
+          // every CTA has read layer l-1's accumulators (it needed x_l for the gate rows it has
+          // now finished): clear this CTA's slice so that layer l+1 can accumulate into them
+          float* accp = ws.acc32 + (size_t)((l - 1) & 1) * kMaxB * H;
+          const int tot = B * H, lo = (int)(((long long)tot * c) / G),
+                    hi = (int)(((long long)tot * (c + 1)) / G);
+          for (int e = lo + lane; e < hi; e += 32) accp[e] = 0.f;
+          __threadfence();
+        }
+        if (ok && l >= 1) ok = mbar_wait(lfree_u + 8u * h, (l - 1) & 1, &s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        int run = 0;
+#pragma unroll
+        for (int q = 0; q < kMegaMaxGrid / 32; ++q) {
+          const int i = q * 32 + lane;
+          int v = cv[q];
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += y;
+          }
+          if (i < G) s_pref[i] = run + v;
+          run += __shfl_sync(0xffffffffu, v, 31);
+        }
+        __syncwarp();
+        CATS_STAMP(2, 2 + 5 * h, tl);
+        const int n = run;
+        const int p0 = (int)(((long long)c * n) / G), p1 = (int)(((long long)(c + 1) * n) / G);
+        const int cnt = ok ? p1 - p0 : 0;
+        const int hlo = half_row0(h, I), hrows = half_row0(h + 1, I) - hlo;
+        for (int j = lane; j < cnt; j += 32) {
+          const int pos = p0 + j;
+          int lo = 0, hi = G - 1;  // smallest segment with s_pref > pos
+          while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (s_pref[mid] > pos) hi = mid; else lo = mid + 1;
+          }
+          const int excl = lo ? s_pref[lo - 1] : 0;
+          const int q = hlo + seg_row0(lo, G, hrows) + (pos - excl);
+          s_idx[h * A.cap + j] = __ldcg(ws.seg_idx + q);
+#pragma unroll
+          for (int t = 0; t < BT; ++t)
+            s_hg[(h * A.cap + j) * BT + t] =
+                (t < B) ? __ldcg(ws.seg_gate + (size_t)q * B + t) : 0.f;
+        }
+        if (lane == 0) {
+          s_cnt[h] = cnt;
+          if (c == 0) {
+            if (h == 0) ws.hdr[HDR_NACTIVE] = n; else ws.hdr[HDR_NACTIVE] += n;
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(lready_u + 8u * h);
+        CATS_STAMP(1, 10 + 3 * h, tl);
+      }
+    }
+  } else {
+    // =========================================================================== consumers
+    // Control-flow rule: every consumer thread executes exactly the same sequence of
+    // consumer_bar_sync() calls whatever happens; `ok` only switches waits and work off.
+    bool ok = true;
+    int k = 0;
+    float acc[NVT][BT][N];
+
+    // x_{l+1} (and, after the last layer, the outputs) from layer l's accumulators.  Every CTA
+    // computes the whole vector for itself; global outputs are written in disjoint slices.
+    auto next_x = [&](int l, bool last) {
+      if (tid == 0 && ok) ok = grid_wait(gbar, gtarget(3 * l + 2), &s_abort);
+      consumer_bar_sync();
+      ok = !s_abort;
+      const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+      const int ngrp = H >> 2;
+      const int own_lo = (int)(((long long)ngrp * c) / G),
+                own_hi = (int)(((long long)ngrp * (c + 1)) / G);
+      const T* nw = reinterpret_cast<const T*>(P.nw[l]);
+      constexpr int KV = 4;
+      for (int b = 0; b < B; ++b) {
+        float ss = 0.f;
+        for (int g0 = 0; g0 < ngrp && ok; g0 += KV * kConsumerThreads) {
+          float4 a[KV];
+#pragma unroll
+          for (int q = 0; q < KV; ++q) {
+            const int g = g0 + q * kConsumerThreads + tid;
+            a[q] = (g < ngrp) ? __ldcg(reinterpret_cast<const float4*>(accp + (size_t)b * H) + g)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int q = 0; q < KV; ++q) {
+            const int g = g0 + q * kConsumerThreads + tid;
+            if (g < ngrp) {
+              const float y[4] = {a[q].x, a[q].y, a[q].z, a[q].w};
+              const bool mine = last && g >= own_lo && g < own_hi;
+              const size_t e = (size_t)b * H + 4 * (size_t)g;
+              if (mine && A.out_last) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  reinterpret_cast<T*>(A.out_last)[e + i] = V::from_f(y[i]);
+              }
+              if (has_resid) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const T rn = V::from_f(V::to_f(rs[e + i]) + y[i]);
+                  rs[e + i] = rn;
+                  const float rf = V::to_f(rn);
+                  ss = fmaf(rf, rf, ss);
+                  if (mine) reinterpret_cast<T*>(A.resid)[e + i] = rn;
+                }
+              }
+            }
+          }
+        }
+        if (has_resid) {
+          ss = warp_sum(ss);
+          consumer_bar_sync();
+          if (lane == 0) s_red[warp] = ss;
+          consumer_bar_sync();
+          float tot = 0.f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) tot += s_red[w];
+          const float rsq = rsqrtf(tot / (float)H + A.eps);
+          for (int g = tid; g < ngrp && ok; g += kConsumerThreads) {
+            const bool mine = last && g >= own_lo && g < own_hi;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const size_t e = (size_t)b * H + 4 * (size_t)g + i;
+              T y = V::from_f(V::to_f(rs[e]) * rsq);
+              if (nw) y = V::from_f(V::to_f(nw[4 * g + i]) * V::to_f(y));
+              xs[e] = y;
+              if (mine && A.x_out) reinterpret_cast<T*>(A.x_out)[e] = y;
+            }
+          }
+        }
+      }
+      consumer_bar_sync();
+    };
+
+    for (int l = 0; l < L; ++l) {
+      const bool tl = (l == L / 2);
+      CATS_STAMP(0, 0, tl && tid == 0);
+      if (l > 0) next_x(l - 1, false);
+      CATS_STAMP(0, 1, tl && tid == 0);
+      const float thr = P.thr[l];
+#pragma unroll
+      for (int g = 0; g < NVT; ++g)
+#pragma unroll
+        for (int t = 0; t < BT; ++t)
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[g][t][i] = 0.f;
+
+      // ---- gate rows of the two halves ---------------------------------------------------------
+      for (int h = 0; h < 2; ++h) {
+        const int r0 = seg_lo(h), R = seg_hi(h) - r0;
+        float* sv = s_val + (size_t)h * A.rmax * BT;
+        if (warp < cw) {
+          int j = ((warp - k) % cw + cw) % cw;  // first j with (k + j) % cw == warp
+          for (; j < R && ok; j += cw) {
+            const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
+            if (!(ok = mbar_wait_warp(full_u + 8u * s, cy & 1, &s_abort))) break;
+            float a1[BT];
+            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_bytes), xs, B,
+                                  H, lane, a1);
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              const float a0 = warp_sum(a1[t]);
+              if (lane == 0) sv[j * BT + t] = silu_f(a0);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_n(empty_u + 8u * s, kConsumerWarps);
+          }
+        }
+        k += R;
+        __syncwarp();
+        CATS_STAMP(0, 2 + h, tl && tid == 0);
+        if (lane == 0) mbar_arrive(gdone_u + 8u * h);
+      }
+
+      // ---- up and down rows of the two halves ----------------------------------------------------
+      for (int h = 0; h < 2; ++h) {
+        CATS_STAMP(0, 6 + 4 * h, tl && tid == 0);
+        if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
+        CATS_STAMP(0, 7 + 4 * h, tl && tid == 0);
+        const int cnt = ok ? s_cnt[h] : 0;
+        float* hg = s_hg + (size_t)h * A.cap * BT;
+        if (warp < cw) {
+          int j = ((warp - k) % cw + cw) % cw;
+          for (; j < cnt && ok; j += cw) {
+            const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
+            if (!(ok = mbar_wait_warp(full_u + 8u * s, cy & 1, &s_abort))) break;
+            float a1[BT];
+            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_bytes), xs, B,
+                                  H, lane, a1);
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              const float a0 = warp_sum(a1[t]);
+              if (lane == 0) hg[j * BT + t] *= a0;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_n(empty_u + 8u * s, kConsumerWarps);
+          }
+        }
+        k += cnt;
+        CATS_STAMP(0, 8 + 4 * h, tl && tid == 0);
+        consumer_bar_sync();  // every h_j of this half is final; all earlier items are consumed
+        ok = !s_abort;
+        // Down rows in groups of kDG: lane q waits for the q-th row of the group (one round trip
+        // to the barrier unit for the whole group instead of one per row), the warp adds the
+        // group's rows, then lane q releases the q-th stage.
+        constexpr int kDG = 8;
+#ifdef CATS_PHASE_TIMING
+        long long dbg_w = 0, dbg_p = 0, dbg_a = 0, dbg_t;
+#endif
+        const int dg = min(kDG, S);  // a group must fit in the ring
+        for (int j0 = 0; j0 < cnt && ok; j0 += dg) {
+          const int nb = min(dg, cnt - j0);
+#ifdef CATS_PHASE_TIMING
+          dbg_t = clock64();
+#endif
+          bool mine = true;
+          if (lane < nb) {
+            const int kk = k + j0 + lane;
+            const int cy = cyc_of(kk);
+            mine = mbar_wait(full_u + 8u * (kk - cy * S), cy & 1, &s_abort);
+          }
+          ok = __all_sync(0xffffffffu, mine);
+          if (!ok) break;
+#ifdef CATS_PHASE_TIMING
+          dbg_w += clock64() - dbg_t; dbg_t = clock64();
+          if (tl && h == 0 && c == 5 && tid == 0 && j0 < 32) cats_trace[0][j0] = cats_now();
+          if (tl && h == 0 && c == 5 && tid == 224 && j0 < 32) cats_trace[1][j0] = cats_now();
+#endif
+          // all loads of a column group first (kDG independent 16-byte loads in flight per
+          // thread), then the FMAs: with two warps per scheduler nothing else hides the latency
+          typename V::Scalar hb[kDG][BT];
+          const uint4* rowp[kDG];
+#pragma unroll
+          for (int q = 0; q < kDG; ++q) {
+            const int qq = q < nb ? q : 0;
+            rowp[q] = reinterpret_cast<const uint4*>(ring + (size_t)slot_of(k + j0 + qq) * row_bytes);
+#pragma unroll
+            for (int t = 0; t < BT; ++t)
+              hb[q][t] = V::prep(q < nb ? hg[(j0 + q) * BT + t] : 0.f);
+          }
+#pragma unroll
+          for (int g = 0; g < NVT; ++g) {
+            const int v = g * kConsumerThreads + tid;
+            if (v < nvec) {
+              uint4 wq[kDG];
+#pragma unroll
+              for (int q = 0; q < kDG; ++q) wq[q] = rowp[q][v];
+#pragma unroll
+              for (int q = 0; q < kDG; ++q)
+#pragma unroll
+                for (int t = 0; t < BT; ++t) V::axpy(hb[q][t], wq[q], acc[g][t]);
+            }
+          }
+          __syncwarp();
+#ifdef CATS_PHASE_TIMING
+          dbg_p += clock64() - dbg_t; dbg_t = clock64();
+#endif
+          if (lane < nb) {
+            const int kk = k + j0 + lane;
+            mbar_arrive(empty_u + 8u * slot_of(kk));
+          }
+#ifdef CATS_PHASE_TIMING
+          dbg_a += clock64() - dbg_t;
+#endif
+        }
+#ifdef CATS_PHASE_TIMING
+        if (tl && h == 0 && c == 5 && lane == 0) { cats_trace[1][32 + warp * 3] = dbg_w; cats_trace[1][33 + warp * 3] = dbg_p; cats_trace[1][34 + warp * 3] = dbg_a; }
+#endif
+        k += cnt;
+        __syncwarp();
+        CATS_STAMP(0, 9 + 4 * h, tl && tid == 0);
+        if (lane == 0 && ok) mbar_arrive(lfree_u + 8u * h);
+      }
+
+      // ---- this CTA's share of the down projection into the layer's fp32 accumulators ----------
+      if (ok) {
+        float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+#pragma unroll
+        for (int g = 0; g < NVT; ++g) {
+          const int v = g * kConsumerThreads + tid;
+          if (v < nvec) {
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              if (t < B) {
+                float* dst = accp + (size_t)t * H + (size_t)v * N;
+#pragma unroll
+                for (int i = 0; i < N; i += 4)
+                  red_add_v4(dst + i, acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2],
+                             acc[g][t][i + 3]);
+              }
+            }
+          }
+        }
+      }
+      __threadfence();
+      consumer_bar_sync();
+      ok = !s_abort;
+      if (tid == 0 && ok) grid_arrive(gbar);
+      CATS_STAMP(0, 14, tl && tid == 0);
+    }
+
+    next_x(L - 1, true);
+    // everyone has read the last layer's accumulators once the final barrier completes
+    __threadfence();
+    consumer_bar_sync();
+    if (tid == 0 && ok) {
+      grid_arrive(gbar);
+      grid_wait(gbar, gtarget(3 * L), &s_abort);
+    }
+    consumer_bar_sync();
+    if (!s_abort) {
+      float* accp = ws.acc32 + (size_t)((L - 1) & 1) * kMaxB * H;
+      const int tot = B * H, lo = (int)(((long long)tot * c) / G),
+                hi = (int)(((long long)tot * (c + 1)) / G);
+      for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
+      if (c == 0 && tid == 0) {
+        ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)(3 * L + 1) * (unsigned)G);
+        ws.hdr[HDR_NSEG] = -1;  // this kernel's segment lists are per half: not resumable
+      }
+    }
+  }
+
+  __syncthreads();
+  if (s_abort) {
+    if (tid == 0) atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_MEGA);
+    drain_after_abort();
+  }
+}
+
+}  // namespace cats

@@ -34,13 +34,19 @@ enum { STATUS_OK = 0, STATUS_WAIT_TIMEOUT_GATE = 1, STATUS_WAIT_TIMEOUT_UPDOWN =
 
 // Optional per-CTA phase timestamps for development builds (compiled out by default).
 #ifdef CATS_PHASE_TIMING
-__device__ unsigned long long cats_stamps[2][256][16];
-__device__ __forceinline__ void cats_stamp(int kernel, int slot) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  cats_stamps[kernel][blockIdx.x][slot] = t;
+__device__ unsigned long long cats_stamps[3][256][16];
+__device__ unsigned long long cats_trace[4][64];  // per-item times of one CTA (development)
+__device__ __forceinline__ unsigned long long cats_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+// predicated store, no branch: a stamp must not make the calling warp diverge
+__device__ __forceinline__ void cats_stamp(int kernel, int slot, bool cond) {
+  unsigned long long* p = &cats_stamps[kernel][blockIdx.x][slot];
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u64 t;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+      "mov.u64 t, %globaltimer;\n\t@p st.global.u64 [%0], t;\n\t}" ::"l"(p),
+      "r"((unsigned)cond)
+      : "memory");
 }
-#define CATS_STAMP(kernel, slot, cond) do { if (cond) cats_stamp(kernel, slot); } while (0)
+#define CATS_STAMP(kernel, slot, cond) cats_stamp(kernel, slot, cond)
 #else
 #define CATS_STAMP(kernel, slot, cond) do { } while (0)
 #endif
@@ -61,11 +67,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// Non-blocking phase test (test_wait, not try_wait: a suspended try_wait of every idle warp keeps
+// the shared-memory pipe busy and slows the warps that are working).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -73,19 +81,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit was hit or another thread of the CTA gave up.
+// Polls back to back for the first few microseconds (ring hand-offs are that short and a sleep,
+// however brief it is asked to be, costs about a microsecond), then backs off.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    const long long dt = clock64() - t0;
+    if (dt > 20000) __nanosleep(100);
+    if (dt > kWaitCycles) {
       *abort = 1;
       return false;
     }
   }
+}
+// Whole-warp wait: lane 0 polls, the result is broadcast.  One polling lane per warp instead of
+// 32 keeps the shared-memory pipe free for the warps that are working (32 lanes polling one
+// barrier word serialise into 32 accesses per poll).  Must be called by a converged warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // 1-D bulk copy global -> shared memory of this CTA, completion on `bar` (no multicast).
 __device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint32_t bytes,
@@ -160,6 +180,43 @@ __device__ __forceinline__ void warp_dot2_smem(const T* w0, const T* w1, const T
     acc[0][t] += odd[0][t];
     acc[1][t] += odd[1][t];
   }
+}
+
+// Dot product of ONE weight row held in shared memory with the B activation vectors (also in
+// shared memory).  Eight vectors are fetched before the first FMA; four partial sums per token.
+template <typename T, int BT>
+__device__ __forceinline__ void warp_dot1_smem(const T* w0, const T* xs, int B, int H, int lane,
+                                               float (&acc)[BT]) {
+  constexpr int N = VecT<T>::N;
+  constexpr int U = 8;
+  const int nvec = H / N;
+  const uint4* p0 = reinterpret_cast<const uint4*>(w0);
+  const uint4* px = reinterpret_cast<const uint4*>(xs);
+  float part[4][BT];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int t = 0; t < BT; ++t) part[q][t] = 0.f;
+  int v = lane;
+  for (; v + 32 * (U - 1) < nvec; v += 32 * U) {
+    uint4 a[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[u] = p0[v + 32 * u];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int t = 0; t < BT; ++t)
+        if (t < B) VecT<T>::fma1(a[u], px[(size_t)t * nvec + v + 32 * u], part[u & 3][t]);
+    }
+  }
+  for (; v < nvec; v += 32) {
+    const uint4 a = p0[v];
+#pragma unroll
+    for (int t = 0; t < BT; ++t)
+      if (t < B) VecT<T>::fma1(a, px[(size_t)t * nvec + v], part[0][t]);
+  }
+#pragma unroll
+  for (int t = 0; t < BT; ++t) acc[t] = (part[0][t] + part[1][t]) + (part[2][t] + part[3][t]);
 }
 
 // Copy the B activation vectors into shared memory (all threads of the CTA).
@@ -245,7 +302,7 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
   } else {
     for (int k = warp; warp < cw && k < nst; k += cw) {
       const int s = k % S;
-      if (!mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort)) break;
+      if (!mbar_wait_warp(full_u + 8u * s, (k / S) & 1, &s_abort)) break;
       const int lr = k * SR;
       const T* w0 = reinterpret_cast<const T*>(ring + (size_t)s * stage_bytes);
 #pragma unroll
@@ -409,7 +466,7 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
     // up rows: warp-strided, one row per visit
     for (int k = warp; warp < cw && k < cnt; k += cw) {
       const int s = k % S;
-      if (!(ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
+      if (!(ok = mbar_wait_warp(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
       float acc[2][BT];
 #pragma unroll
       for (int t = 0; t < BT; ++t) acc[0][t] = acc[1][t] = 0.f;
@@ -437,7 +494,7 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
         for (int t = 0; t < BT; ++t) acc[g][i][t] = 0.f;
     for (int k = cnt; k < nitems && ok; ++k) {
       const int s = k % S;
-      ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort);
+      ok = mbar_wait_warp(full_u + 8u * s, (k / S) & 1, &s_abort);
       if (ok) {
         const uint4* row = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
         float hb[BT];

@@ -66,9 +66,11 @@ int cats_sm_count(void);
 /*
  * Tuning knob, process-wide.  "tma" (0/1): use the TMA-fed kernels where the shape allows
  * (default 1; 0 forces the direct-load kernels).  "ring_kb": shared-memory ring per TMA kernel in
- * KiB (default 200).  "pdl" (0/1): launch with programmatic dependent launch (default 1).  The
- * same values are read once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB and
- * CATS_B200_PDL.  No reference
+ * KiB (default 200).  "pdl" (0/1): launch with programmatic dependent launch (default 1).
+ * "mega" (0/1): run cats_mlp / cats_mlp_stack as one persistent cooperative kernel where the
+ * shape allows (default 1; 0 = one stage-1 and one stage-2/3 launch per layer).  The same values
+ * are read once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL
+ * and CATS_B200_MEGA.  No reference
  * counterpart.
  */
 int cats_set_option(const char* name, int value);
