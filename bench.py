@@ -44,6 +44,10 @@ WORKLOADS = {
     "llama7b_fp32": ("llama7b", torch.float32, 32, 0.5),
     "llama70b": ("llama70b", torch.bfloat16, 80, 0.7),
 }
+# dram__bytes_read + dram__bytes_write per layer of k_cats_mega for the default workload, from the
+# ncu capture summarised in profiles/k_cats_mega_mistral7b_fp16_s50_ncu_full.md (2 layers captured;
+# traffic is proportional to the number of layers)
+NCU_TRAFFIC_PER_LAYER = {("mistral7b", 0.5, 1): 236.8e6}
 METRIC = "cats_mlp_stack_decode_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -269,7 +273,7 @@ def per_launch_us(launch_one, n_items, repeats, stream):
 def run_gpu_arm(args):
     import torch.distributed as dist
 
-    from cats_b200 import ops, synth, tp
+    from cats_b200 import _lib, ops, synth, tp
     from cats_b200.stack import CatsMLPStack
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -349,22 +353,20 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_e2e = float(t.item())
 
-    # ---- per-kernel launch durations and roofline (rank 0's own kernels) ---------------------
+    # ---- roofline of the kernel that ran in the timed region ------------------------------------
+    # Algorithmic bytes of one layer: all of Wg, the active rows of Wu and WdT, x in, out.
     ws = stack.ws
     xin = x0.reshape(B, 1, H).clone()
     out = torch.empty_like(xin)
-    counts = []
-    for l in layers[: min(L, 8)]:
-        ops.gate(xin, l.wg, l.threshold, ws=ws)
-        counts.append(ws.counters()[0])
+    if world == 1:
+        stack.set_input(x0)
+        counts = stack.active_counts()
+    else:
+        counts = []
+        for l in layers[: min(L, 8)]:
+            ops.gate(xin, l.wg, l.threshold, ws=ws)
+            counts.append(ws.counters()[0])
     n_act = statistics.mean(counts)
-    reps = max(1, min(10, 320 // L))
-    gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
-                            L, reps, stream)
-    # stage 2+3 consumes the list of the last stage-1 launch (same input, same sparsity level)
-    ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
-    updown_us = per_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
-                              L, reps, stream)
     bytes_gate = esize * I_local * H + esize * B * H
     bytes_updown = 2 * esize * n_act * H + 2 * esize * B * H
     bytes_layer = bytes_gate + bytes_updown
@@ -373,23 +375,40 @@ def run_gpu_arm(args):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    kernels = {
-        "k_gate": {"us": gate_us[0], "us_median": gate_us[1], "bytes": bytes_gate,
-                   "GBps": bytes_gate / gate_us[0] / 1e3},
-        "k_updown": {"us": updown_us[0], "us_median": updown_us[1], "bytes": bytes_updown,
-                     "GBps": bytes_updown / updown_us[0] / 1e3},
-    }
-    dom = max(kernels, key=lambda k: kernels[k]["us"])
     us_layer = ms_step * 1e3 / L
+    mega = world == 1 and _lib.lib().cats_uses_persistent_kernel(L, B, H, I_local, ops.dtype_code(dtype)) == 1
+    # the two staged kernels on their own (single launches bracketed by events, rotating over the
+    # layers): what a caller of the stage-level entry points gets, and the pre-fusion baseline
+    reps = max(1, min(10, 320 // L))
+    gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
+                            L, reps, stream)
+    ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
+    updown_us = per_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
+                              L, reps, stream)
+    staged = {
+        "k_gate_tma": {"us": gate_us[0], "bytes": bytes_gate, "GBps": bytes_gate / gate_us[0] / 1e3},
+        "k_updown_tma": {"us": updown_us[0], "bytes": bytes_updown,
+                         "GBps": bytes_updown / updown_us[0] / 1e3},
+    }
+    if mega:
+        # one launch of the persistent kernel = one step = L layers
+        kname, launch_us, launch_bytes = "k_cats_mega", ms_step * 1e3, bytes_layer * L
+    else:
+        kname = max(staged, key=lambda k: staged[k]["us"])
+        launch_us, launch_bytes = staged[kname]["us"], staged[kname]["bytes"]
+    achieved = launch_bytes / launch_us / 1e3
     roofline = {
-        "bound": "hbm", "kernel": dom, "achieved": kernels[dom]["GBps"], "peak": peak,
-        "unit": "GB/s", "frac": kernels[dom]["GBps"] / peak, "peak_source": peak_src,
-        "traffic": None, "bytes_per_launch": kernels[dom]["bytes"],
-        "launch_us": kernels[dom]["us"], "kernels": kernels,
+        "bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak, "peak_source": peak_src,
+        "traffic": (NCU_TRAFFIC_PER_LAYER[(args.workload, s, B)] * L
+                    if mega and (args.workload, s, B) in NCU_TRAFFIC_PER_LAYER else None),
+        "bytes_per_launch": launch_bytes, "launch_us": launch_us,
+        "units_per_launch": f"{L} layers" if mega else "1 layer stage",
+        "frac_of_8TBps_nominal": achieved / 8000.0,
         "layer": {"bytes": bytes_layer, "us": us_layer, "GBps": bytes_layer / us_layer / 1e3,
                   "frac": bytes_layer / us_layer / 1e3 / peak,
                   "frac_of_8TBps": bytes_layer / us_layer / 1e3 / 8000.0},
-        "n_active_mean": n_act, "intermediate_local": I_local,
+        "staged_kernels": staged, "n_active_mean": n_act, "intermediate_local": I_local,
     }
 
     # ---- dense cuBLAS MLP of the same shape (context; single GPU only) -----------------------
@@ -447,7 +466,7 @@ def run_gpu_arm(args):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "CatsMLPStack.decode_step (pinned host in/out, cats_mlp_stack C call)"
                 if world == 1 else "TPStack (CUDA graph of kernels + NCCL all-reduce)"},
-        "gpu_launches": args.steps * stack.launches_per_step,
+        "gpu_launches": args.steps * (1 if mega else stack.launches_per_step),
         "roofline": roofline, "clocks": clocks.summary(), "dense_cublas": dense,
         "cpu_baseline": cpu,
     }

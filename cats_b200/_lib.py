@@ -48,6 +48,7 @@ SIGNATURES = {
                                 ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_float), _c_void_p,
                                 _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
                                 _c_int, _c_int, _c_float, _c_void_p]),
+    "cats_uses_persistent_kernel": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int]),
     "cats_down_dense": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                  _c_void_p]),
     "cats_tail": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_int, _c_int,

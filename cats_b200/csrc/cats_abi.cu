@@ -678,6 +678,11 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
   return CATS_OK;
 }
 
+int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype) {
+  if (check_common(B, H, I, dtype)) return 0;
+  return plan_mega(L, B, H, I, dtype, true).ok ? 1 : 0;
+}
+
 int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int dtype, void* out,
                     void* stream) {
   // rows of Wd [H, I] have length I: the vector-width rule applies to I here

@@ -167,6 +167,13 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
                    size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream);
 
 /*
+ * 1 if cats_mlp_stack runs these L layers as ONE persistent cooperative launch on the current
+ * device (shape, batch and options permitting), 0 if it launches two kernels per layer.
+ * For reporting (benchmarks count their kernel launches with it).  No reference counterpart.
+ */
+int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype);
+
+/*
  * Dense down projection over Wd [H, I] (nn.Linear layout): out[b,h] = sum_i Wd[h,i] * inter[b,i].
  * Reads all of Wd whatever the sparsity; exists for callers that cannot supply WdT.
  * Replaces gemv_local_kernel (fuse_gemv_cmp_cuda.cu:1786-1960).
