@@ -6,6 +6,8 @@
 
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "cats_mega.cuh"
 
 namespace {
@@ -492,6 +494,9 @@ const char* cats_status_string(int status) {
     case CATS_ERR_WORKSPACE: return "workspace is smaller than cats_workspace_bytes(B, H, I)";
     case CATS_ERR_CUDA: return "CUDA error at launch";
     case CATS_ERR_MODE: return "unsupported mode or flag combination";
+    case CATS_ERR_STATIC_LIMIT:
+      return "shape needs more scratch than the built-in array of cats_mlp_static holds "
+             "(see cats_mlp_static_limit); use cats_mlp with a caller-provided workspace";
     default: return "unknown status";
   }
 }
@@ -681,6 +686,67 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
 int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype) {
   if (check_common(B, H, I, dtype)) return 0;
   return plan_mega(L, B, H, I, dtype, true).ok ? 1 : 0;
+}
+
+// ---- entry point for callers that cannot allocate device memory --------------------------------
+// Scratch for cats_mlp_static lives in this file-scope array: it is part of the loaded module, so
+// every GPU that loads the library carries it until the process exits, and nobody ever has to
+// allocate it.  kStaticWsBytes is the documented limit of that entry point.
+constexpr size_t kStaticWsBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+
+namespace {
+// In host code `g_static_ws` is only a handle for the runtime, not an address a kernel can use:
+// the device address has to be asked for, once per device, with that device current.
+void* g_static_ws_dev[64];
+bool g_static_ws_ready[64];
+std::mutex g_static_ws_mutex;
+
+int static_ws_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= 64) return CATS_ERR_SHAPE;
+  std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+  if (!g_static_ws_ready[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_ws);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (!ptr) return CATS_ERR_NULL;
+    g_static_ws_dev[dev] = ptr;
+    g_static_ws_ready[dev] = true;
+  }
+  *out = g_static_ws_dev[dev];
+  return CATS_OK;
+}
+}  // namespace
+
+size_t cats_mlp_static_limit(void) { return kStaticWsBytes; }
+
+int cats_mlp_static(const void* x, const void* Wg, const void* Wu, const void* WdT, int B, int H,
+                    int I, int dtype, float threshold, void* out, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wg || !Wu || !WdT || !out) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(WdT) || !aligned16(out))
+    return CATS_ERR_ALIGN;
+  // the size check comes first: a shape whose scratch does not fit is refused, never truncated
+  if (ws_layout(nullptr, H, I, nullptr) > kStaticWsBytes) return CATS_ERR_STATIC_LIMIT;
+  void* base = nullptr;
+  if ((s = static_ws_for_current_device(&base))) return s;
+  WsPtrs p;
+  ws_layout(base, H, I, &p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array still holds whatever the previous call (of any caller) left in it.  What the
+  // kernels need to find zero is cleared here, in stream order: the header (completion ticket,
+  // status word) and the fp32 accumulators of the B tokens.
+  cudaError_t e = cudaMemsetAsync(p.hdr, 0, sizeof(int) * kHdrInts, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p.acc32, 0, sizeof(float) * (size_t)B * H, st);
+  if (e != cudaSuccess) return cuda_status(e);
+  e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st);
+  if (e != cudaSuccess) return cuda_status(e);
+  return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, CATS_OUT_STORE, nullptr,
+                               nullptr, nullptr, 0.f, nullptr, st));
 }
 
 int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int dtype, void* out,

@@ -41,7 +41,8 @@ enum {
   CATS_ERR_NULL = -4,       /* a required pointer is NULL */
   CATS_ERR_WORKSPACE = -5,  /* workspace too small for (B, H, I) */
   CATS_ERR_CUDA = -6,       /* CUDA runtime reported an error at launch; see cats_last_cuda_error */
-  CATS_ERR_MODE = -7        /* unknown mode / flag combination */
+  CATS_ERR_MODE = -7,       /* unknown mode / flag combination */
+  CATS_ERR_STATIC_LIMIT = -8 /* cats_mlp_static: shape needs more scratch than its built-in array */
 };
 
 /* how cats_down / cats_updown / cats_mlp deliver the result */
@@ -153,6 +154,39 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
              size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
              int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
              void* stream);
+
+/*
+ * cats_mlp for callers that are not able to allocate device memory.
+ *
+ * Who that is: code that runs where cudaMalloc is off limits or not reachable at all - a plugin
+ * that is handed input and output buffers by a host application and owns no allocator of its own,
+ * a runtime that forbids allocation after start-up (fixed memory budgets, real-time loops), a
+ * binding in a language where wrapping one more device buffer is more trouble than it is worth.
+ * cats_mlp needs a workspace from the caller; this entry point brings its own: an 8 MiB array
+ * that is compiled into the library (a `static __device__` array), so every GPU that loads the
+ * library holds it until the process ends and nothing is allocated at any time - no cudaMalloc,
+ * no cudaFree, no allocating library call.  The caller passes only inputs and the output.
+ *
+ * Limit: the scratch of a shape is cats_workspace_bytes(B, H, I); shapes that need more than
+ * cats_mlp_static_limit() bytes (8 MiB: hidden 8192 x intermediate 28672 still fits) are refused
+ * with CATS_ERR_STATIC_LIMIT before anything is launched.
+ *
+ * Rules of use:
+ *   - The first call on a device looks up the array's device address (once per device, with that
+ *     device current).  Make that first call before you start capturing a stream.
+ *   - All calls on one device share the one array and it keeps the previous call's contents; each
+ *     call clears, in stream order, the parts that have to start at zero.  Two calls that overlap
+ *     on the GPU (different streams, no ordering between them) race on it: keep the calls of a
+ *     device in one stream or order them with events.
+ *   - out[B, H] has the element type dtype and is overwritten; arguments as for cats_mlp.
+ * This entry point has no counterpart in the reference (its ops allocate their scratch with
+ * cudaMalloc on every call).
+ */
+int cats_mlp_static(const void* x, const void* Wg, const void* Wu, const void* WdT, int B, int H,
+                    int I, int dtype, float threshold, void* out, void* stream);
+
+/* Size in bytes of the built-in scratch array of cats_mlp_static. */
+size_t cats_mlp_static_limit(void);
 
 /*
  * A stack of L CATS MLP layers chained through the fused residual + RMS-norm tail, launched

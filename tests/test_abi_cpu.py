@@ -45,7 +45,8 @@ def test_workspace_size_is_monotonic_and_covers_lists():
 
 
 @pytest.mark.parametrize("status,needle", [(-1, "dtype"), (-2, "shape"), (-3, "aligned"),
-                                           (-4, "NULL"), (-5, "workspace"), (-7, "mode")])
+                                           (-4, "NULL"), (-5, "workspace"), (-7, "mode"),
+                                           (-8, "cats_mlp_static")])
 def test_status_strings(status, needle):
     assert needle.lower() in _lib.lib().cats_status_string(status).decode().lower()
 
