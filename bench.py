@@ -445,9 +445,18 @@ def run_gpu_arm(args):
                  "what": "torch F.linear x3 + SiLU*mul + residual/RMS-norm per layer, CUDA graph",
                  "speedup_of_cats": ms_dense / ms_step}
 
-    if rank != 0:
+    def leave():
+        """Multi-rank exit: a last barrier, then leave without tearing NCCL down — destroying the
+        process group while a captured CUDA graph still references its collectives can block."""
         if world > 1:
-            dist.destroy_process_group()
+            torch.cuda.synchronize()
+            dist.barrier()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
 
     cpu = None
@@ -471,8 +480,7 @@ def run_gpu_arm(args):
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 def main():

@@ -18,7 +18,7 @@
 // "last CTA" epilogue), and the next layer's gate rows are already streaming while that happens.
 //
 // Roles in a CTA (416 threads): warps 0-7 consumers; warps 8-11 producers (one elected thread
-// each issues cp.async.bulk row copies, global -> this CTA's shared memory, never multicast; one
+// each issues cp.async.bulk row copies, global -> this CTA's shared memory, plain single-CTA form; one
 // thread manages a copy roughly every 240 ns, a quarter of what an SM's HBM share needs at 8 KB
 // rows, hence four); warp 12 control (compacts and publishes the segment's active list, waits
 // for the grid barriers, scans the segment counts, fills the CTA's work list).

@@ -3,7 +3,7 @@
 // A GEMV has one FMA per weight element, so the only thing that matters is how many bytes each
 // SM keeps in flight towards HBM.  Here one elected producer thread per CTA issues 1-D bulk
 // copies (cp.async.bulk global -> this CTA's shared memory, completion counted on an mbarrier;
-// never the cluster-multicast form) of whole weight rows into a ring of stages, and eight
+// always the plain single-CTA form) of whole weight rows into a ring of stages, and eight
 // consumer warps do the arithmetic out of shared memory.  Bytes in flight = ring size, decided by
 // the host, independent of register allocation and occupancy.  One CTA per SM per kernel; the
 // rings of the stage-1 kernel and the stage-2/3 kernel together fit one SM, so with programmatic
@@ -107,7 +107,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
-// 1-D bulk copy global -> shared memory of this CTA, completion on `bar` (no multicast).
+// 1-D bulk copy global -> shared memory of this CTA, completion on `bar` (plain single-CTA form).
 __device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint32_t bytes,
                                             uint32_t bar) {
   asm volatile(
