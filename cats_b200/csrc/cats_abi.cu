@@ -99,7 +99,8 @@ int batch_tile(int B) { return B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : B <= 8 ? 8
     default: return FN<T, 16>(__VA_ARGS__);       \
   }
 #ifdef CATS_DEV_HALF_ONLY
-#define CATS_DISPATCH(dtype, BT_, FN, ...) return FN<__half, 1>(__VA_ARGS__)
+#define CATS_DISPATCH(dtype, BT_, FN, ...) \
+  do { if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__); return FN<__half, 2>(__VA_ARGS__); } while (0)
 #else
 #define CATS_DISPATCH(dtype, BT_, FN, ...)                                     \
   do {                                                                         \
@@ -333,15 +334,15 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   p.nvt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
   p.grid = dev_info().sms;
   if (p.grid > kMegaMaxGrid) p.grid = kMegaMaxGrid;
-  if (p.grid > I / 2) p.grid = I / 2;
+  if (p.grid > I / kParts) p.grid = I / kParts;
   if (p.grid < 1) return p;
-  const int half_rows = (I + 1) / 2;
+  const int half_rows = (I + kParts - 1) / kParts;
   p.rmax = (half_rows + p.grid - 1) / p.grid + 1;
   p.cap = p.rmax;
   const int bt = batch_tile(B);
   const size_t fixed = 16 + (size_t)B * row_bytes * (has_resid ? 2 : 1) +
-                       2 * sizeof(float) * (size_t)p.rmax * bt + 2 * sizeof(int) * (size_t)p.cap +
-                       2 * sizeof(float) * (size_t)p.cap * bt;
+                       kParts * (sizeof(float) * (size_t)p.rmax * bt + sizeof(int) * (size_t)p.cap +
+                                 sizeof(float) * (size_t)p.cap * bt);
   const size_t limit = (size_t)dev_info().max_smem_optin;
   const size_t statics = 2048;  // static shared memory of the kernel + slack
   if (limit < fixed + statics + 2 * row_bytes + 1024) return p;
@@ -361,7 +362,7 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
     }
   }
   if (p.S < 2) return p;
-  p.smem = align_up((size_t)p.S * row_bytes + 8 * (size_t)(2 * p.S + 6), 16) + fixed;
+  p.smem = align_up((size_t)p.S * row_bytes + 8 * (size_t)(2 * p.S + 3 * kParts + 1), 16) + fixed;
   p.ok = p.smem + statics <= limit;
   return p;
 }
@@ -400,7 +401,8 @@ cudaError_t run_mega(const MegaPlan& p, const MegaParams& P, const MegaArgs& A, 
 
 // B <= 4 only (the TMA kernels are instantiated for batch tiles 1, 2, 4)
 #ifdef CATS_DEV_HALF_ONLY  // development builds: one instantiation, quick to compile
-#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...) return FN<__half, 1>(__VA_ARGS__)
+#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...) \
+  do { if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__); return FN<__half, 2>(__VA_ARGS__); } while (0)
 #else
 #define CATS_DISPATCH_TMA(dtype, BT_, FN, ...)                                   \
   do {                                                                           \

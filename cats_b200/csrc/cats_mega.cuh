@@ -6,14 +6,14 @@
 // that is ~20 us per layer of HBM idling.  Here one CTA per SM stays resident for the whole
 // stack and keeps one stream of weight rows flowing through a shared-memory ring:
 //
-//   per layer:   G(0) G(1) U(0) D(0) U(1) D(1)        (G gate rows, U up rows, D down rows)
+//   per layer:   G(0) G(1) G(2) U(0) D(0) U(1) D(1) U(2) D(2)    (G gate, U up, D down rows)
 //
-// The layer's neurons are split into two halves.  G(h) are the gate rows of this CTA's segment
-// of half h; after them the CTA publishes the segment's active list and arrives at a grid
-// barrier.  U(h)/D(h) are this CTA's balanced share of the active neurons of half h over ALL
-// CTAs, known once that barrier has completed.  Because G(1) is streamed between G(0) and U(0),
-// and U(0)/D(0) between G(1) and U(1), the barrier + scan latency of each half is covered by the
-// other half's rows: the producers normally never wait for a list.  The residual add and RMS
+// The layer's neurons are split into three parts.  G(p) are the gate rows of this CTA's segment
+// of part p; after them the CTA publishes the segment's active list and arrives at a grid
+// barrier.  U(p)/D(p) are this CTA's balanced share of the active neurons of part p over ALL
+// CTAs, known once that barrier has completed.  Between G(p) and U(p) the stream always carries
+// two other phases' rows (about 10 us), which covers compaction + fence + barrier + scan (about
+// 6-9 us, measured): the producers normally never wait for a list.  (With two halves they did.)  The residual add and RMS
 // norm between layers are computed by every CTA for itself from the fp32 accumulators (no
 // "last CTA" epilogue), and the next layer's gate rows are already streaming while that happens.
 //
@@ -21,7 +21,11 @@
 // each issues cp.async.bulk row copies, global -> this CTA's shared memory, plain single-CTA form; one
 // thread manages a copy roughly every 240 ns, a quarter of what an SM's HBM share needs at 8 KB
 // rows, hence four); warp 12 control (compacts and publishes the segment's active list, waits
-// for the grid barriers, scans the segment counts, fills the CTA's work list).
+// for the grid barriers, scans the segment counts, fills the CTA's work list).  The control work
+// is split over two warps - a publisher (compaction, publication, barrier arrival) and a lister
+// (barrier wait, scan, list fill, clearing of the accumulators) - because every global fence
+// costs several microseconds while the copy ring keeps HBM saturated, and one warp doing both
+// chains in sequence was too slow to have the lists ready in time.
 //
 // Waits.  CTAs wait for one another at grid barriers, so the launch is cooperative (all CTAs
 // co-resident or the launch fails).  Every wait (mbarrier or grid barrier) is bounded (~1 s):
@@ -37,12 +41,21 @@ namespace cats {
 constexpr int kMegaMaxLayers = 112;
 constexpr int kMegaMaxGrid = 256;
 constexpr int kMegaProducers = 4;  // issuing threads (one per warp); the host uses 2 when 4 does not divide S
-constexpr int kMegaWarps = kConsumerWarps + kMegaProducers + 1;
+constexpr int kMegaWarps = kConsumerWarps + kMegaProducers + 2;  // + publisher + lister
 constexpr int kMegaThreads = kMegaWarps * 32;
-constexpr int kSegHalfStride = kMaxSeg / 2;  // seg_count slots of half 1 start here
+constexpr int kParts = 3;                      // a layer's neurons are processed in this many parts
+constexpr int kSegHalfStride = kMaxSeg / 4;   // seg_count slots of part p start at p * this
 
 enum { STATUS_WAIT_TIMEOUT_MEGA = 3 };
-enum { HDR_GBAR = 8, HDR_GBAR_BASE = 9 };
+// Grid-barrier counters.  A counting barrier is only sound when no CTA can arrive for its next
+// use before the current one has completed.  Publishing part h of layer l+1 needs x_{l+1}, which
+// needs every CTA's down rows of layer l, which need every part's list of layer l: so one counter
+// per part is safe, while one counter shared by the parts is not (a fast CTA's arrival for part
+// h+1 would be counted towards part h while a slow CTA has not published yet).  The layer
+// barrier (one arrival per consumer warp) has its own counter.  The *_BASE slots hold the
+// counters' values at the start of the current launch.
+enum { HDR_GBAR = 8 /* [kParts] */, HDR_OBAR = 12, HDR_GBAR_BASE = 13, HDR_OBAR_BASE = 14 };
+static_assert(HDR_GBAR + kParts <= HDR_OBAR, "one list-barrier counter per part");
 
 struct MegaParams {
   const void* wg[kMegaMaxLayers];
@@ -65,9 +78,16 @@ struct MegaArgs {
 };
 
 // Rows [lo, hi) of half h out of I.
-__host__ __device__ inline int half_row0(int h, int I) { return (int)(((long long)I * h) / 2); }
+__host__ __device__ inline int half_row0(int h, int I) {
+  return (int)(((long long)I * h) / kParts);
+}
 
 // ---- grid barrier on a monotonic counter ------------------------------------------------------
+// Arrival with release semantics at GPU scope.  It is always executed by lane 0 of a warp right
+// after __syncwarp(), and everything the arrival publishes was written by lanes of that same
+// warp, so this one fence is the only one on the path (an explicit __threadfence() by every
+// writer plus a release here would pay the fence twice, and a fence costs microseconds while
+// the copy ring saturates HBM).
 __device__ __forceinline__ void grid_arrive(unsigned* ctr) {
   asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
 }
@@ -103,7 +123,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   __shared__ float s_red[32];
-  __shared__ int s_cnt[2];
+  __shared__ int s_cnt[kParts];
   __shared__ int s_pref[kMegaMaxGrid];
 
   const int L = A.L, B = A.B, H = A.H, I = A.I, S = A.S, cw = A.cw;
@@ -121,37 +141,44 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   unsigned char* ring = smem;
   size_t off = (size_t)S * row_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off);
-  off += 8 * (size_t)(2 * S + 6);
+  off += 8 * (size_t)(2 * S + 3 * kParts + 1);
   off = align_up(off, 16);
   T* xs = reinterpret_cast<T*>(smem + off);
   off += (size_t)B * row_bytes;
   T* rs = reinterpret_cast<T*>(smem + off);
   off += has_resid ? (size_t)B * row_bytes : 0;
-  float* s_val = reinterpret_cast<float*>(smem + off);  // [2][rmax * BT]
-  off += 2 * sizeof(float) * (size_t)A.rmax * BT;
-  int* s_idx = reinterpret_cast<int*>(smem + off);  // [2][cap]
-  off += 2 * sizeof(int) * (size_t)A.cap;
-  float* s_hg = reinterpret_cast<float*>(smem + off);  // [2][cap * BT]
+  float* s_val = reinterpret_cast<float*>(smem + off);  // [kParts][rmax * BT]
+  off += kParts * sizeof(float) * (size_t)A.rmax * BT;
+  int* s_idx = reinterpret_cast<int*>(smem + off);  // [kParts][cap]
+  off += kParts * sizeof(int) * (size_t)A.cap;
+  float* s_hg = reinterpret_cast<float*>(smem + off);  // [kParts][cap * BT]
 
   const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(bars), empty_u = full_u + 8u * S;
-  const uint32_t lready_u = empty_u + 8u * S, lfree_u = lready_u + 16u, gdone_u = lfree_u + 16u;
+  const uint32_t lready_u = empty_u + 8u * S, lfree_u = lready_u + 8u * kParts,
+                 gdone_u = lfree_u + 8u * kParts, zdone_u = gdone_u + 8u * kParts;
 
   unsigned* gbar = reinterpret_cast<unsigned*>(ws.hdr + HDR_GBAR);
+  unsigned* obar = reinterpret_cast<unsigned*>(ws.hdr + HDR_OBAR);
   const unsigned gbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_GBAR_BASE));
-  auto gtarget = [&](int idx) { return gbase + (unsigned)(idx + 1) * (unsigned)G; };
-  // barrier indices: 3*l + h after the gate rows of half h, 3*l + 2 after the layer's down rows,
-  // 3*L at the very end
+  const unsigned obase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_OBAR_BASE));
+  // list barrier of (l, h): counter h, G arrivals per layer; layer barrier idx = l, final = L
+  // (kConsumerWarps * G arrivals: every consumer warp arrives for itself)
+  auto gtarget = [&](int l) { return gbase + (unsigned)(l + 1) * (unsigned)G; };
+  auto otarget = [&](int idx) {
+    return obase + (unsigned)(idx + 1) * (unsigned)(G * kConsumerWarps);
+  };
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full_u + 8u * s, 1);
       mbar_init(empty_u + 8u * s, kConsumerWarps);
     }
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < kParts; ++h) {
       mbar_init(lready_u + 8u * h, 1);
       mbar_init(lfree_u + 8u * h, kConsumerWarps);
       mbar_init(gdone_u + 8u * h, kConsumerWarps);
     }
+    mbar_init(zdone_u, 1);
     s_abort = 0;
     mbar_fence_init();
   }
@@ -191,52 +218,59 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         const T* Wg = reinterpret_cast<const T*>(P.wg[l]);
         const T* Wu = reinterpret_cast<const T*>(P.wu[l]);
         const T* Wd = reinterpret_cast<const T*>(P.wdt[l]);
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < kParts && ok; ++h) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
-          for (int j = 0; j < R && ok; ++j)
-            if ((k + j) % npw == p) issue(k + j, Wg + (size_t)(r0 + j) * H);
+          // own items only: j == (p - k) mod npw, stepping by npw (no division per row)
+          for (int j = ((p - k) % npw + npw) % npw; j < R && ok; j += npw) {
+#ifdef CATS_PHASE_TIMING
+            if ((l == L / 2) && h == 1 && c == 5 && j < 64) cats_trace[4][j] = cats_now();
+#endif
+            issue(k + j, Wg + (size_t)(r0 + j) * H);
+#ifdef CATS_PHASE_TIMING
+            if ((l == L / 2) && h == 1 && c == 5 && j < 64) cats_trace[5][j] = cats_now();
+#endif
+          }
           k += R;
-          CATS_STAMP(1, 1 + h, tl);
+          CATS_STAMP(1, 1 + h, tl && h < 2);
         }
-        for (int h = 0; h < 2 && ok; ++h) {
+        for (int h = 0; h < kParts && ok; ++h) {
           if (!mbar_wait(lready_u + 8u * h, l & 1, &s_abort)) {
             ok = false;
             break;
           }
-          CATS_STAMP(1, 3 + 2 * h, tl);
+          CATS_STAMP(1, 3 + 2 * h, tl && h < 2);
           const int cnt = s_cnt[h];
           const int* idx = s_idx + h * A.cap;
-          for (int j = 0; j < cnt && ok; ++j)
-            if ((k + j) % npw == p) issue(k + j, Wu + (size_t)idx[j] * H);
+          for (int j = ((p - k) % npw + npw) % npw; j < cnt && ok; j += npw)
+            issue(k + j, Wu + (size_t)idx[j] * H);
           k += cnt;
-          for (int j = 0; j < cnt && ok; ++j)
-            if ((k + j) % npw == p) {
+          for (int j = ((p - k) % npw + npw) % npw; j < cnt && ok; j += npw) {
 #ifdef CATS_PHASE_TIMING
-              if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[2][j] = cats_now();
+            if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[2][j] = cats_now();
 #endif
-              issue(k + j, Wd + (size_t)idx[j] * H);
+            issue(k + j, Wd + (size_t)idx[j] * H);
 #ifdef CATS_PHASE_TIMING
-              if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[3][j] = cats_now();
+            if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[3][j] = cats_now();
 #endif
-            }
+          }
           k += cnt;
-          CATS_STAMP(1, 4 + 2 * h, tl);
+          CATS_STAMP(1, 4 + 2 * h, tl && h < 2);
         }
       }
     }
   } else if (warp == kConsumerWarps + kMegaProducers) {
-    // =========================================================================== control
-    // Warp-uniform control flow on purpose: every lane polls in the waits and nothing is done
-    // under `if (lane == 0)` except single stores.  (With lane-0-only waits and early exits the
-    // warp ran its shuffles diverged, which made this section ~40x slower.)
+    // =========================================================================== publisher
+    // Warp-uniform control flow on purpose (every lane polls in the waits): with lane-0-only
+    // waits and early exits the warp ran its shuffles diverged, ~40x slower.
     bool ok = true;
     for (int l = 0; l < L; ++l) {
       const float thr = P.thr[l];
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < kParts; ++h) {
         const bool tl = (l == L / 2) && lane == 0;
-        // ---- this CTA's gate values of half h are in: ballot / popc compaction, publish, arrive
+        // this CTA's gate values of part h are in: ballot / popc compaction, publish, arrive
         if (ok) ok = mbar_wait(gdone_u + 8u * h, l & 1, &s_abort);
         ok = __all_sync(0xffffffffu, ok);
+        CATS_STAMP(2, 4 + 5 * h, tl && h < 2);
         if (ok) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
           const float* sv = s_val + (size_t)h * A.rmax * BT;
@@ -266,30 +300,34 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             base += __popc(m);
           }
           if (lane == 0) ws.seg_count[h * kSegHalfStride + c] = base;
-          __threadfence();
+          // the lister's clearing of the accumulators that layer l will add into must be
+          // complete (and fenced) before this CTA lets the barrier of (l, 0) complete
+          if (h == 0 && l >= 2) ok = mbar_wait(zdone_u, (l - 2) & 1, &s_abort);
+          ok = __all_sync(0xffffffffu, ok);
+          CATS_STAMP(2, 0 + 5 * h, tl && h < 2);
           __syncwarp();
-          if (lane == 0) grid_arrive(gbar);
+          if (lane == 0 && ok) grid_arrive(gbar + h);
+          CATS_STAMP(2, 1 + 5 * h, tl && h < 2);
         }
-        CATS_STAMP(1, 8 + 3 * h, tl);
-        // ---- all CTAs have published half h: scan the counts, take this CTA's balanced share
-        if (ok) ok = grid_wait(gbar, gtarget(3 * l + h), &s_abort);
+        CATS_STAMP(1, 8 + 3 * h, tl && h < 2);
+      }
+    }
+  } else if (warp == kConsumerWarps + kMegaProducers + 1) {
+    // =========================================================================== lister
+    bool ok = true;
+    for (int l = 0; l < L; ++l) {
+      for (int h = 0; h < kParts; ++h) {
+        const bool tl = (l == L / 2) && lane == 0;
+        // all CTAs have published part h: scan the counts, take this CTA's balanced share
+        if (ok) ok = grid_wait(gbar + h, gtarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
-        CATS_STAMP(1, 9 + 3 * h, tl);
+        CATS_STAMP(1, 9 + 3 * h, tl && h < 2);
         const int* cntp = ws.seg_count + h * kSegHalfStride;
         int cv[kMegaMaxGrid / 32];
 #pragma unroll
         for (int q = 0; q < kMegaMaxGrid / 32; ++q) {  // all loads first: one L2 round trip
           const int i = q * 32 + lane;
           cv[q] = (ok && i < G) ? __ldcg(cntp + i) : 0;
-        }
-        if (ok && h == 0 && l >= 1) {
-          // every CTA has read layer l-1's accumulators (it needed x_l for the gate rows it has
-          // now finished): clear this CTA's slice so that layer l+1 can accumulate into them
-          float* accp = ws.acc32 + (size_t)((l - 1) & 1) * kMaxB * H;
-          const int tot = B * H, lo = (int)(((long long)tot * c) / G),
-                    hi = (int)(((long long)tot * (c + 1)) / G);
-          for (int e = lo + lane; e < hi; e += 32) accp[e] = 0.f;
-          __threadfence();
         }
         if (ok && l >= 1) ok = mbar_wait(lfree_u + 8u * h, (l - 1) & 1, &s_abort);
         ok = __all_sync(0xffffffffu, ok);
@@ -307,7 +345,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           run += __shfl_sync(0xffffffffu, v, 31);
         }
         __syncwarp();
-        CATS_STAMP(2, 2 + 5 * h, tl);
+        CATS_STAMP(2, 2 + 5 * h, tl && h < 2);
         const int n = run;
         const int p0 = (int)(((long long)c * n) / G), p1 = (int)(((long long)(c + 1) * n) / G);
         const int cnt = ok ? p1 - p0 : 0;
@@ -335,7 +373,20 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         }
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(lready_u + 8u * h);
-        CATS_STAMP(1, 10 + 3 * h, tl);
+        CATS_STAMP(1, 10 + 3 * h, tl && h < 2);
+      }
+      if (l >= 1) {
+        // Every CTA has read layer l-1's accumulators (it needed x_l for gate rows that are
+        // published by now): clear this CTA's slice so that layer l+1 can add into them.
+        if (ok) {
+          float* accp = ws.acc32 + (size_t)((l - 1) & 1) * kMaxB * H;
+          const int tot = B * H, lo = (int)(((long long)tot * c) / G),
+                    hi = (int)(((long long)tot * (c + 1)) / G);
+          for (int e = lo + lane; e < hi; e += 32) accp[e] = 0.f;
+          __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(zdone_u);
       }
     }
   } else {
@@ -349,7 +400,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // x_{l+1} (and, after the last layer, the outputs) from layer l's accumulators.  Every CTA
     // computes the whole vector for itself; global outputs are written in disjoint slices.
     auto next_x = [&](int l, bool last) {
-      if (tid == 0 && ok) ok = grid_wait(gbar, gtarget(3 * l + 2), &s_abort);
+      if (tid == 0 && ok) ok = grid_wait(obar, otarget(l), &s_abort);
       consumer_bar_sync();
       ok = !s_abort;
       const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
@@ -432,7 +483,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           for (int i = 0; i < N; ++i) acc[g][t][i] = 0.f;
 
       // ---- gate rows of the two halves ---------------------------------------------------------
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < kParts; ++h) {
         const int r0 = seg_lo(h), R = seg_hi(h) - r0;
         float* sv = s_val + (size_t)h * A.rmax * BT;
         if (warp < cw) {
@@ -440,6 +491,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           for (; j < R && ok; j += cw) {
             const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
             if (!(ok = mbar_wait_warp(full_u + 8u * s, cy & 1, &s_abort))) break;
+#ifdef CATS_PHASE_TIMING
+            if (tl && h == 1 && c == 5 && lane == 0 && j < 64) cats_trace[6][j] = cats_now();
+#endif
             float a1[BT];
             warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_bytes), xs, B,
                                   H, lane, a1);
@@ -450,19 +504,22 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_n(empty_u + 8u * s, kConsumerWarps);
+#ifdef CATS_PHASE_TIMING
+            if (tl && h == 1 && c == 5 && lane == 0 && j < 64) cats_trace[7][j] = cats_now();
+#endif
           }
         }
         k += R;
         __syncwarp();
-        CATS_STAMP(0, 2 + h, tl && tid == 0);
+        CATS_STAMP(0, 2 + h, tl && tid == 0 && h < 2);
         if (lane == 0) mbar_arrive(gdone_u + 8u * h);
       }
 
       // ---- up and down rows of the two halves ----------------------------------------------------
-      for (int h = 0; h < 2; ++h) {
-        CATS_STAMP(0, 6 + 4 * h, tl && tid == 0);
+      for (int h = 0; h < kParts; ++h) {
+        CATS_STAMP(0, 6 + 4 * h, tl && tid == 0 && h < 2);
         if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
-        CATS_STAMP(0, 7 + 4 * h, tl && tid == 0);
+        CATS_STAMP(0, 7 + 4 * h, tl && tid == 0 && h < 2);
         const int cnt = ok ? s_cnt[h] : 0;
         float* hg = s_hg + (size_t)h * A.cap * BT;
         if (warp < cw) {
@@ -483,7 +540,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           }
         }
         k += cnt;
-        CATS_STAMP(0, 8 + 4 * h, tl && tid == 0);
+        CATS_STAMP(0, 8 + 4 * h, tl && tid == 0 && h < 2);
         consumer_bar_sync();  // every h_j of this half is final; all earlier items are consumed
         ok = !s_abort;
         // Down rows in groups of kDG: lane q waits for the q-th row of the group (one round trip
@@ -554,7 +611,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
 #endif
         k += cnt;
         __syncwarp();
-        CATS_STAMP(0, 9 + 4 * h, tl && tid == 0);
+        CATS_STAMP(0, 9 + 4 * h, tl && tid == 0 && h < 2);
         if (lane == 0 && ok) mbar_arrive(lfree_u + 8u * h);
       }
 
@@ -578,21 +635,17 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           }
         }
       }
-      __threadfence();
-      consumer_bar_sync();
-      ok = !s_abort;
-      if (tid == 0 && ok) grid_arrive(gbar);
+      // every warp publishes its own share of the sums: no CTA barrier, one fence per warp
+      __syncwarp();
+      if (lane == 0 && ok) grid_arrive(obar);
       CATS_STAMP(0, 14, tl && tid == 0);
     }
 
     next_x(L - 1, true);
     // everyone has read the last layer's accumulators once the final barrier completes
-    __threadfence();
-    consumer_bar_sync();
-    if (tid == 0 && ok) {
-      grid_arrive(gbar);
-      grid_wait(gbar, gtarget(3 * L), &s_abort);
-    }
+    __syncwarp();
+    if (lane == 0 && ok) grid_arrive(obar);
+    if (tid == 0 && ok) grid_wait(obar, otarget(L), &s_abort);
     consumer_bar_sync();
     if (!s_abort) {
       float* accp = ws.acc32 + (size_t)((L - 1) & 1) * kMaxB * H;
@@ -600,7 +653,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
                 hi = (int)(((long long)tot * (c + 1)) / G);
       for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
       if (c == 0 && tid == 0) {
-        ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)(3 * L + 1) * (unsigned)G);
+        ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)L * (unsigned)G);
+        ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
         ws.hdr[HDR_NSEG] = -1;  // this kernel's segment lists are per half: not resumable
       }
     }

@@ -35,7 +35,7 @@ enum { STATUS_OK = 0, STATUS_WAIT_TIMEOUT_GATE = 1, STATUS_WAIT_TIMEOUT_UPDOWN =
 // Optional per-CTA phase timestamps for development builds (compiled out by default).
 #ifdef CATS_PHASE_TIMING
 __device__ unsigned long long cats_stamps[3][256][16];
-__device__ unsigned long long cats_trace[4][64];  // per-item times of one CTA (development)
+__device__ unsigned long long cats_trace[8][64];  // per-item times of one CTA (development)
 __device__ __forceinline__ unsigned long long cats_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 // predicated store, no branch: a stamp must not make the calling warp diverge
 __device__ __forceinline__ void cats_stamp(int kernel, int slot, bool cond) {

@@ -165,6 +165,46 @@ def test_stages_one_by_one_equal_the_fused_call(cuda_device):
         assert O.rel_l2(to_np(acc) - 1.0, ref["out"]) <= OUT_TOL[dt]
 
 
+def test_lists_left_by_an_earlier_call_are_never_read(cuda_device):
+    """The kernels keep their active lists in the workspace between stages.  A call must only read
+    lists it wrote itself: overwrite them with garbage between calls (and change the batch size,
+    which changes their layout) and the results must not move.  The accumulators and the header
+    (which must stay clean between calls) are left alone."""
+    from cats_b200 import ops
+
+    dev, dt = cuda_device, torch.float16
+    up = lambda v: (v + 255) // 256 * 256
+    for H, I in [(64, 160), (64, 1000), (1024, 2752), (4096, 14336)]:
+        ws = ops.get_workspace(dev, H, I)
+        # workspace layout (cats_common.cuh, ws_layout): header, segment counts, accumulators,
+        # then the list arrays; every array starts on a 256-byte boundary
+        o_cnt = 256
+        o_acc = o_cnt + 4 * 1024
+        o_idx = up(o_acc + 4 * 2 * 16 * H)
+        o_gate = up(o_idx + 4 * I)
+        o_flat = up(o_gate + 4 * I * 16)
+        o_h = up(o_flat + 4 * I)
+        o_end = up(o_h + 4 * I * 16)
+        assert o_end == ws.nbytes
+        for B in (1, 2, 1, 4):
+            x, layer = synth_case(H, I, B, dt, 0.5, 11 + B, dev)
+            ref = O.dense_masked_mlp(to_np(x).reshape(B, H), to_np(layer.wg), to_np(layer.wu),
+                                     to_np(layer.wdt).T, layer.threshold)
+            for rep in range(3):
+                ws.buf[o_cnt:o_acc].view(torch.int32).fill_(1 + rep)
+                for lo, hi in ((o_idx, o_gate), (o_flat, o_h)):      # indices: a valid row
+                    ws.buf[lo:hi].view(torch.int32).fill_(rep)
+                for lo, hi in ((o_gate, o_flat), (o_h, o_end)):      # values: large
+                    ws.buf[lo:hi].view(torch.float32).fill_(1000.0 * rep)
+                out = ops.mlp(x, layer.wg, layer.wu, layer.wdt, layer.threshold, ws=ws)
+                torch.cuda.synchronize()
+                err = O.rel_l2(to_np(out).reshape(B, H), ref["out"])
+                assert err <= 1e-2, (H, I, B, rep, err)
+                n_active, status = ws.counters()
+                assert status == 0
+                assert abs(n_active - int(O.union_mask(ref["mask"]).sum())) <= 2, (H, I, B, rep)
+
+
 def test_fused_residual_and_rmsnorm_tail(cuda_device):
     from cats_b200 import ops
 
