@@ -67,6 +67,8 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-dense", action="store_true")
+    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: exchange inside the persistent kernel, or one NCCL all-reduce per layer")
     return ap.parse_args()
 
 
@@ -234,7 +236,7 @@ def config_block(args, H, I, dtype, L, s, world):
                      f"{str(dtype).replace('torch.', '')}, sparsity {s}, batch {args.batch}, decode"),
         "layers": L, "hidden": H, "intermediate": I, "sparsity": s, "batch": args.batch,
         "parallelism": "single GPU" if world == 1 else f"tp{world} over the intermediate dimension, "
-                                                       "one all-reduce per layer",
+                                                       "one exchange of partial sums per layer",
         "l2": "inputs larger than L2: every step streams the distinct weights of all layers "
               "(GBs) once, nothing is reused between layers or steps",
         "seed": args.seed,
@@ -306,9 +308,29 @@ def run_gpu_arm(args):
         stack.x_host.copy_(x0.cpu())
         run = stack.run_device
     else:
-        stack = tp.TPStack(layers, batch=B)
-        stack.set_input(x0)
-        stack.capture()
+        # product path: one persistent kernel per GPU exchanging partial sums over NVLink itself;
+        # the kernels + NCCL all-reduce graph only if that cannot be set up on every rank
+        tp_mode, why = "fused", ""
+        stack = None
+        if args.tp == "fused":
+            try:
+                stack = tp.FusedTPStack(layers, batch=B)
+                stack.set_input(x0)
+                stack.run_device()
+                torch.cuda.synchronize()
+                if stack.device_status() != 0:
+                    raise RuntimeError("device status %d" % stack.device_status())
+            except Exception as e:  # noqa: BLE001 - reported in the JSON line
+                why, stack = f"{type(e).__name__}: {e}"[:200], None
+            okf = torch.tensor([1 if stack is not None else 0], device=dev)
+            dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+            if int(okf.item()) == 0:
+                stack = None
+        if stack is None:
+            tp_mode = "nccl" if args.tp == "nccl" else f"nccl (fused unavailable: {why or 'on another rank'})"
+            stack = tp.TPStack(layers, batch=B)
+            stack.set_input(x0)
+            stack.capture()
         run = stack.run_device
         x_host = x0.cpu().pin_memory()
         out_host = torch.empty_like(x_host).pin_memory()
@@ -376,7 +398,28 @@ def run_gpu_arm(args):
     else:
         peak, peak_src = 6650.0, "fallback"
     us_layer = ms_step * 1e3 / L
-    mega = world == 1 and _lib.lib().cats_uses_persistent_kernel(L, B, H, I_local, ops.dtype_code(dtype)) == 1
+    if world == 1:
+        mega = _lib.lib().cats_uses_persistent_kernel(L, B, H, I_local, ops.dtype_code(dtype)) == 1
+    else:
+        mega = isinstance(stack, tp.FusedTPStack)
+        if mega and stack.device_status() != 0:
+            raise RuntimeError("a bounded wait ran out inside the tensor-parallel kernel")
+    # tensor parallel: the all-reduce variant timed beside the fused kernel (context)
+    nccl_variant = None
+    if world > 1 and mega and not args.no_dense:
+        ref_stack = tp.TPStack(layers, batch=B)
+        ref_stack.set_input(x0)
+        ref_stack.capture()
+        for _ in range(3):
+            ref_stack.run_device()
+        barrier()
+        ms_ref = event_time_ms(ref_stack.run_device, max(5, args.steps // 4), stream)
+        barrier()
+        t = torch.tensor([ms_ref], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nccl_variant = {"us_per_layer": float(t.item()) * 1e3 / L,
+                        "what": "stage kernels + one NCCL all-reduce + tail per layer, CUDA graph",
+                        "speedup_of_fused": float(t.item()) / ms_step}
     # the two staged kernels on their own (single launches bracketed by events, rotating over the
     # layers): what a caller of the stage-level entry points gets, and the pre-fusion baseline
     reps = max(1, min(10, 320 // L))
@@ -474,11 +517,14 @@ def run_gpu_arm(args):
         "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "CatsMLPStack.decode_step (pinned host in/out, cats_mlp_stack C call)"
-                if world == 1 else "TPStack (CUDA graph of kernels + NCCL all-reduce)"},
+                if world == 1 else ("FusedTPStack (pinned host in/out, one cats_tp_mlp_stack C call per rank)"
+                                    if mega else "TPStack (CUDA graph of kernels + NCCL all-reduce)")},
         "gpu_launches": args.steps * (1 if mega else stack.launches_per_step),
         "roofline": roofline, "clocks": clocks.summary(), "dense_cublas": dense,
         "cpu_baseline": cpu,
     }
+    if world > 1:
+        line["tp"] = {"mode": tp_mode, "nccl_allreduce_variant": nccl_variant}
     print(json.dumps(line), flush=True)
     leave()
 

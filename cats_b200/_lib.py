@@ -14,6 +14,9 @@ from . import _build
 
 F32, F16, BF16 = 0, 1, 2
 OUT_STORE, OUT_ACC_F32 = 0, 1
+# status codes of include/cats_b200.h
+OK, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_NULL = 0, -1, -2, -3, -4
+ERR_WORKSPACE, ERR_CUDA, ERR_MODE, ERR_STATIC_LIMIT = -5, -6, -7, -8
 MAX_BATCH = 16
 
 _c_void_p = ctypes.c_void_p
@@ -51,6 +54,16 @@ SIGNATURES = {
                                 ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_float), _c_void_p,
                                 _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
                                 _c_int, _c_int, _c_float, _c_void_p]),
+    "cats_tp_exchange_bytes": (_c_size_t, [_c_int]),
+    "cats_tp_exchange_alloc": (_c_int, [_c_int, ctypes.POINTER(_c_void_p), ctypes.c_char_p]),
+    "cats_tp_exchange_open": (_c_int, [ctypes.c_char_p, ctypes.POINTER(_c_void_p)]),
+    "cats_tp_exchange_close": (_c_int, [_c_void_p]),
+    "cats_tp_exchange_free": (_c_int, [_c_void_p]),
+    "cats_tp_mlp_stack": (_c_int, [_c_int, ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
+                                   ctypes.POINTER(_c_void_p), ctypes.POINTER(ctypes.c_float),
+                                   _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
+                                   _c_int, _c_int, ctypes.c_float, _c_int, _c_int,
+                                   ctypes.POINTER(_c_void_p), _c_void_p]),
     "cats_uses_persistent_kernel": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int]),
     "cats_down_dense": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                  _c_void_p]),

@@ -685,6 +685,81 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
   return CATS_OK;
 }
 
+// ---- tensor-parallel stack: compute and exchange in one persistent kernel per GPU --------------
+size_t cats_tp_exchange_bytes(int H) { return H > 0 ? xchg_bytes(H) : 0; }
+
+int cats_tp_exchange_alloc(int H, void** ptr, unsigned char* handle64) {
+  if (!ptr || !handle64) return CATS_ERR_NULL;
+  if (H <= 0) return CATS_ERR_SHAPE;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle is passed around as 64 bytes");
+  void* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, xchg_bytes(H));
+  if (e == cudaSuccess) e = cudaMemset(d, 0, xchg_bytes(H));
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+  if (e != cudaSuccess) {
+    if (d) cudaFree(d);
+    return cuda_status(e);
+  }
+  memcpy(handle64, &h, 64);
+  *ptr = d;
+  return CATS_OK;
+}
+
+int cats_tp_exchange_open(const unsigned char* handle64, void** ptr) {
+  if (!ptr || !handle64) return CATS_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return cuda_status(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int cats_tp_exchange_close(void* ptr) {
+  return ptr ? cuda_status(cudaIpcCloseMemHandle(ptr)) : CATS_ERR_NULL;
+}
+
+int cats_tp_exchange_free(void* ptr) { return ptr ? cuda_status(cudaFree(ptr)) : CATS_ERR_NULL; }
+
+int cats_tp_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const void* const* WdT,
+                      const float* thresholds, void* x_io, void* resid, void* ws, size_t ws_bytes,
+                      int B, int H, int I_local, int dtype, float eps, int nranks, int rank,
+                      void* const* exchange, void* stream) {
+  int s = check_common(B, H, I_local, dtype);
+  if (s) return s;
+  if (L < 1 || nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks || B > kMegaMaxB)
+    return CATS_ERR_SHAPE;
+  if (!Wg || !Wu || !WdT || !thresholds || !x_io || !resid || !exchange) return CATS_ERR_NULL;
+  if (!aligned16(x_io) || !aligned16(resid)) return CATS_ERR_ALIGN;
+  for (int l = 0; l < L; ++l) {
+    if (!Wg[l] || !Wu[l] || !WdT[l]) return CATS_ERR_NULL;
+    if (!aligned16(Wg[l]) || !aligned16(Wu[l]) || !aligned16(WdT[l])) return CATS_ERR_ALIGN;
+  }
+  for (int p = 0; p < nranks; ++p) {
+    if (!exchange[p]) return CATS_ERR_NULL;
+    if (((uintptr_t)exchange[p]) % 256) return CATS_ERR_ALIGN;
+  }
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I_local, &p))) return s;
+  const MegaPlan mp = plan_mega(L, B, H, I_local, dtype, true);
+  // every rank has to run the same grid (the arrival counts are per source rank): one CTA per
+  // SM, which needs at least that many rows per part
+  if (!mp.ok || mp.grid != dev_info().sms) return CATS_ERR_MODE;
+  MegaParams P;
+  for (int l = 0; l < L; ++l) {
+    P.wg[l] = Wg[l];
+    P.wu[l] = Wu[l];
+    P.wdt[l] = WdT[l];
+    P.nw[l] = nullptr;
+    P.thr[l] = thresholds[l];
+  }
+  MegaArgs A;
+  memset(&A, 0, sizeof(A));
+  A.L = L; A.B = B; A.H = H; A.I = I_local; A.eps = eps;
+  A.x_in = x_io; A.x_out = x_io; A.resid = resid; A.out_last = nullptr;
+  A.nranks = nranks; A.rank = rank;
+  for (int q = 0; q < nranks; ++q) A.xchg[q] = static_cast<unsigned char*>(exchange[q]);
+  return cuda_status(do_mega(mp, P, A, p, dtype, static_cast<cudaStream_t>(stream)));
+}
+
 int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype) {
   if (check_common(B, H, I, dtype)) return 0;
   return plan_mega(L, B, H, I, dtype, true).ok ? 1 : 0;

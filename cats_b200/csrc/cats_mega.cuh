@@ -40,6 +40,7 @@ namespace cats {
 
 constexpr int kMegaMaxLayers = 112;
 constexpr int kMegaMaxGrid = 256;
+constexpr int kMaxRanks = 8;                   // GPUs of one tensor-parallel group
 constexpr int kMegaProducers = 4;  // issuing threads (one per warp); the host uses 2 when 4 does not divide S
 constexpr int kMegaWarps = kConsumerWarps + kMegaProducers + 2;  // + publisher + lister
 constexpr int kMegaThreads = kMegaWarps * 32;
@@ -75,7 +76,27 @@ struct MegaArgs {
   void* x_out;       // [B,H] normalised residual after the last layer (needs resid), or null
   void* resid;       // [B,H] residual stream in/out, or null (then L must be 1)
   void* out_last;    // [B,H] raw MLP output of the last layer, or null
+  // Tensor parallelism over the intermediate dimension: nranks GPUs each run this kernel on
+  // their own row slice and exchange the layers' partial sums through `xchg` (xchg[p] = rank
+  // p's exchange buffer as mapped into this process; xchg[rank] is local).  nranks == 0: none.
+  int nranks, rank;
+  unsigned char* xchg[kMaxRanks];
 };
+
+// Exchange buffer of one rank (see MegaArgs::xchg).  Header: one arrival counter per SOURCE rank
+// (a source's CTAs arrive once per layer, after their stores into this buffer), the counters'
+// common value at the start of the current launch, and the running number of layers (its low
+// bit selects the slot set, so consecutive layers alternate sets across launches too).
+// Then slots[2][kMaxRanks][kMegaMaxB * H] fp32: slots[s][p] = rank p's partial sums.
+enum { XCH_ARRIVED = 0 /* [kMaxRanks] */, XCH_BASE = 16, XCH_LAYERS = 17, XCH_HDR_BYTES = 256 };
+constexpr int kMegaMaxB = 4;
+__host__ __device__ inline size_t xchg_bytes(int H) {
+  return XCH_HDR_BYTES + sizeof(float) * 2 * (size_t)kMaxRanks * kMegaMaxB * H;
+}
+__host__ __device__ inline float* xchg_slot(unsigned char* base, int set, int src, int H) {
+  return reinterpret_cast<float*>(base + XCH_HDR_BYTES) +
+         ((size_t)set * kMaxRanks + src) * kMegaMaxB * H;
+}
 
 // Rows [lo, hi) of half h out of I.
 __host__ __device__ inline int half_row0(int h, int I) {
@@ -109,6 +130,35 @@ __device__ __forceinline__ bool grid_wait(const unsigned* ctr, unsigned target,
     }
     if (*abort) return false;
     if (clock64() - t0 > kWaitCycles) {
+      *abort = 1;
+      return false;
+    }
+  }
+}
+
+// The same pair at system scope, for counters that other GPUs add to over NVLink (the counter
+// polled is always in this GPU's own memory).  Other ranks' kernels are launched by other
+// processes, so the bound is several times the local one.
+__device__ __forceinline__ void peer_arrive(unsigned* ctr) {
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool peer_wait(const unsigned* ctr, unsigned target,
+                                          volatile int* abort) {
+  if ((int)(ld_acquire_sys(ctr) - target) >= 0) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if ((int)(ld_acquire_sys(ctr) - target) >= 0) return true;
+      __nanosleep(40);
+    }
+    if (*abort) return false;
+    if (clock64() - t0 > 4 * kWaitCycles) {
       *abort = 1;
       return false;
     }
@@ -167,6 +217,16 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   auto otarget = [&](int idx) {
     return obase + (unsigned)(idx + 1) * (unsigned)(G * kConsumerWarps);
   };
+
+  // tensor-parallel exchange (K == 0: single GPU)
+  const int K = A.nranks;
+  unsigned* xflag = K ? reinterpret_cast<unsigned*>(A.xchg[A.rank]) : nullptr;
+  const unsigned xbase = K ? __ldcg(xflag + XCH_BASE) : 0u;
+  const unsigned xl0 = K ? __ldcg(xflag + XCH_LAYERS) : 0u;
+  // this CTA's slice (groups of 4 columns) of a [B, H] vector
+  const int ngrp_all = H >> 2;
+  const int own_lo = (int)(((long long)ngrp_all * c) / G),
+            own_hi = (int)(((long long)ngrp_all * (c + 1)) / G);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -302,7 +362,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           if (lane == 0) ws.seg_count[h * kSegHalfStride + c] = base;
           // the lister's clearing of the accumulators that layer l will add into must be
           // complete (and fenced) before this CTA lets the barrier of (l, 0) complete
-          if (h == 0 && l >= 2) ok = mbar_wait(zdone_u, (l - 2) & 1, &s_abort);
+          if (h == 0 && l >= 2 && !K) ok = mbar_wait(zdone_u, (l - 2) & 1, &s_abort);
           ok = __all_sync(0xffffffffu, ok);
           CATS_STAMP(2, 0 + 5 * h, tl && h < 2);
           __syncwarp();
@@ -375,7 +435,30 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (lane == 0 && ok) mbar_arrive(lready_u + 8u * h);
         CATS_STAMP(1, 10 + 3 * h, tl && h < 2);
       }
-      if (l >= 1) {
+      if (K) {
+        // Tensor parallel: once every CTA of this GPU has added its share of layer l, send this
+        // CTA's slice of the sums to every rank's slot for this rank (plain stores into peer
+        // memory; the release at system scope by the arriving lanes publishes them), and clear
+        // the slice for layer l+2 (nobody else reads the accumulators in this mode).
+        if (ok) ok = grid_wait(obar, otarget(l), &s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+          const int set = (int)((xl0 + (unsigned)l) & 1u);
+          for (int b = 0; b < B; ++b) {
+            for (int g = own_lo + lane; g < own_hi; g += 32) {
+              float4* src = reinterpret_cast<float4*>(accp + (size_t)b * H) + g;
+              const float4 v = __ldcg(src);
+              *src = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int p = 0; p < K; ++p)
+                reinterpret_cast<float4*>(xchg_slot(A.xchg[p], set, A.rank, H) + (size_t)b * H)[g] = v;
+            }
+          }
+          __syncwarp();
+          if (lane < K)
+            peer_arrive(reinterpret_cast<unsigned*>(A.xchg[lane]) + XCH_ARRIVED + A.rank);
+        }
+      } else if (l >= 1) {
         // Every CTA has read layer l-1's accumulators (it needed x_l for gate rows that are
         // published by now): clear this CTA's slice so that layer l+1 can add into them.
         if (ok) {
@@ -400,13 +483,20 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // x_{l+1} (and, after the last layer, the outputs) from layer l's accumulators.  Every CTA
     // computes the whole vector for itself; global outputs are written in disjoint slices.
     auto next_x = [&](int l, bool last) {
-      if (tid == 0 && ok) ok = grid_wait(obar, otarget(l), &s_abort);
+      // single GPU: all CTAs' sums are in the accumulators once the layer barrier completes;
+      // tensor parallel: every rank's partial sums are in this GPU's slots once every source
+      // rank's G CTAs have arrived (thread p polls source p's counter)
+      if (K) {
+        if (tid < K && ok) peer_wait(xflag + XCH_ARRIVED + tid, xbase + (unsigned)(l + 1) * G, &s_abort);
+      } else {
+        if (tid == 0 && ok) grid_wait(obar, otarget(l), &s_abort);
+      }
       consumer_bar_sync();
       ok = !s_abort;
-      const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
-      const int ngrp = H >> 2;
-      const int own_lo = (int)(((long long)ngrp * c) / G),
-                own_hi = (int)(((long long)ngrp * (c + 1)) / G);
+      const float* accp = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H)
+                            : ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+      const size_t src_stride = (size_t)kMegaMaxB * H;  // between source ranks' slots
+      const int ngrp = ngrp_all;
       const T* nw = reinterpret_cast<const T*>(P.nw[l]);
       constexpr int KV = 4;
       for (int b = 0; b < B; ++b) {
@@ -418,6 +508,28 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             const int g = g0 + q * kConsumerThreads + tid;
             a[q] = (g < ngrp) ? __ldcg(reinterpret_cast<const float4*>(accp + (size_t)b * H) + g)
                               : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          // the other ranks' partial sums, in rank order on every GPU (identical x everywhere);
+          // four sources' loads in flight at a time
+          for (int p0 = 1; p0 < K; p0 += 4) {
+            float4 t[4][KV];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp)
+#pragma unroll
+              for (int q = 0; q < KV; ++q) {
+                const int g = g0 + q * kConsumerThreads + tid;
+                t[pp][q] = (p0 + pp < K && g < ngrp)
+                               ? __ldcg(reinterpret_cast<const float4*>(
+                                            accp + (size_t)(p0 + pp) * src_stride + (size_t)b * H) + g)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp)
+#pragma unroll
+              for (int q = 0; q < KV; ++q) {
+                a[q].x += t[pp][q].x; a[q].y += t[pp][q].y;
+                a[q].z += t[pp][q].z; a[q].w += t[pp][q].w;
+              }
           }
 #pragma unroll
           for (int q = 0; q < KV; ++q) {
@@ -648,11 +760,17 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     if (tid == 0 && ok) grid_wait(obar, otarget(L), &s_abort);
     consumer_bar_sync();
     if (!s_abort) {
-      float* accp = ws.acc32 + (size_t)((L - 1) & 1) * kMaxB * H;
-      const int tot = B * H, lo = (int)(((long long)tot * c) / G),
-                hi = (int)(((long long)tot * (c + 1)) / G);
-      for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
+      if (!K) {
+        float* accp = ws.acc32 + (size_t)((L - 1) & 1) * kMaxB * H;
+        const int tot = B * H, lo = (int)(((long long)tot * c) / G),
+                  hi = (int)(((long long)tot * (c + 1)) / G);
+        for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
+      }
       if (c == 0 && tid == 0) {
+        if (K) {
+          xflag[XCH_BASE] = xbase + (unsigned)L * (unsigned)G;
+          xflag[XCH_LAYERS] = xl0 + (unsigned)L;
+        }
         ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)L * (unsigned)G);
         ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
         ws.hdr[HDR_NSEG] = -1;  // this kernel's segment lists are per half: not resumable

@@ -10,6 +10,12 @@ multi-GPU inference mode is HF ``device_map="auto"`` layer placement,
 experiments/bench_sparse_inference_llama.py:36); masks per slice are identical to the unsharded
 run because nothing crosses ranks before the sum.
 
+``FusedTPStack`` is the product path: ONE persistent kernel per GPU and token
+(``cats_tp_mlp_stack``) whose CTAs push their slice of the layer's partial sums into every peer's
+exchange buffer over NVLink and add the ranks' partials themselves — no collective library call,
+no kernel boundary between layers.  ``TPStack`` (kernels + one NCCL all-reduce per layer in a CUDA
+graph) is kept as the baseline it is measured against.
+
 ``shard_rows`` / ``shard_layer`` are pure tensor slicing and run anywhere; ``TPStack`` drives the
 CUDA kernels and a torch.distributed process group.  ``local_mlp`` can be replaced (the CPU tests
 plug in a reference implementation to check the sharding algebra under gloo).
@@ -114,3 +120,107 @@ class TPStack:
             self.graph.replay()
         else:
             self._layers_once()
+
+
+class ExchangeBuffers:
+    """One exchange buffer per rank for ``cats_tp_mlp_stack``: this rank's own (allocated and
+    cleared by the library) and the peers' mapped through CUDA IPC handles that travel over the
+    process group's host channel (``all_gather_object``)."""
+
+    def __init__(self, H: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from . import _lib
+
+        L = _lib.lib()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            _lib.check(L.cats_tp_exchange_alloc(H, ctypes.byref(own), handle), "exchange alloc")
+        self.own = own.value
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.ptrs = []
+        for p in range(self.world):
+            if p == self.rank:
+                self.ptrs.append(self.own)
+                continue
+            q = ctypes.c_void_p()
+            with torch.cuda.device(device):
+                _lib.check(L.cats_tp_exchange_open(handles[p], ctypes.byref(q)),
+                           f"exchange open (rank {p})")
+            self.ptrs.append(q.value)
+        self.array = (ctypes.c_void_p * self.world)(*self.ptrs)
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free the own one (all ranks, after their last launch)."""
+        from . import _lib
+
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p, ptr in enumerate(self.ptrs):
+                if p != self.rank and ptr:
+                    L.cats_tp_exchange_close(ptr)
+            if dist.is_initialized() and self.world > 1:
+                dist.barrier()
+            if self.own:
+                L.cats_tp_exchange_free(self.own)
+        self.ptrs, self.own = [], None
+
+
+class FusedTPStack:
+    """Decode loop of L sharded CATS MLP layers as one persistent kernel per GPU and token, the
+    ranks exchanging partial sums inside the kernel.  Same interface as ``TPStack``."""
+
+    def __init__(self, layers: Sequence[Layer], batch: int = 1, eps: float = 1e-6,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from . import _lib, ops
+
+        self.layers: List[Layer] = list(layers)
+        self.L = len(self.layers)
+        self.H = self.layers[0].wg.shape[1]
+        self.I_local = self.layers[0].wg.shape[0]
+        if any(l.wg.shape[0] != self.I_local for l in self.layers):
+            raise RuntimeError("cats_b200.tp: every layer needs the same number of local rows")
+        self.dtype, self.device = self.layers[0].wg.dtype, self.layers[0].wg.device
+        self.B, self.eps, self.group = batch, eps, group
+        z = lambda: torch.zeros((batch, self.H), dtype=self.dtype, device=self.device)
+        self.x, self.resid = z(), z()
+        self.ws = ops.Workspace(self.device, self.H, self.I_local)
+        self.xb = ExchangeBuffers(self.H, self.device, group)
+        arr = lambda ts: (ctypes.c_void_p * self.L)(*[t.data_ptr() for t in ts])
+        self._wg, self._wu = arr([l.wg for l in self.layers]), arr([l.wu for l in self.layers])
+        self._wd = arr([l.wdt for l in self.layers])
+        self._thr = (ctypes.c_float * self.L)(*[float(l.threshold) for l in self.layers])
+        self._dt = ops.dtype_code(self.dtype)
+        self.launches_per_step = 1
+
+    def set_input(self, x: torch.Tensor) -> None:
+        self.x.copy_(x.reshape(self.B, self.H), non_blocking=True)
+        self.resid.copy_(self.x, non_blocking=True)
+
+    def capture(self) -> None:  # one launch per token already
+        pass
+
+    def run_device(self) -> None:
+        from . import _lib
+
+        with torch.cuda.device(self.device):
+            st = _lib.lib().cats_tp_mlp_stack(
+                self.L, self._wg, self._wu, self._wd, self._thr, self.x.data_ptr(),
+                self.resid.data_ptr(), self.ws.ptr, self.ws.nbytes, self.B, self.H, self.I_local,
+                self._dt, float(self.eps), self.xb.world, self.xb.rank, self.xb.array,
+                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "cats_tp_mlp_stack")
+
+    def device_status(self) -> int:
+        return self.ws.counters()[1]
+
+    def close(self) -> None:
+        self.xb.close()

@@ -201,6 +201,41 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
                    size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream);
 
 /*
+ * Tensor parallelism over the intermediate dimension, compute and exchange in ONE kernel per GPU.
+ * Rank r of nranks (<= 8, one process per GPU of one NVLink-connected node) holds rows
+ * [I*r/nranks, I*(r+1)/nranks) of every layer's Wg, Wu and WdT (I_local rows; the thresholds are
+ * the unsharded ones) and runs cats_tp_mlp_stack at the same time as its peers: the persistent
+ * kernel of cats_mlp_stack, whose CTAs, at the end of every layer, store their slice of this
+ * rank's partial sums straight into every peer's exchange buffer over NVLink (plain peer stores
+ * published by a release at system scope; no TMA involved), wait until every rank's partials
+ * have arrived in their own buffer, and add them in rank order, so that every rank computes
+ * bit-identical residuals and inputs for the next layer.  x_io / resid [B, H] as for
+ * cats_mlp_stack, replicated on every rank.  B <= 4.
+ *
+ * exchange[p] (host array of nranks device pointers) is rank p's exchange buffer as mapped into
+ * the calling process; exchange[rank] is the caller's own.  Every rank creates its buffer with
+ * cats_tp_exchange_alloc (cudaMalloc + clear + CUDA IPC handle, 64 bytes), passes the handle to
+ * its peers by any host channel, and maps theirs with cats_tp_exchange_open.  All ranks must make
+ * the same sequence of cats_tp_mlp_stack calls (same L, B, H) on a set of buffers.
+ * A rank whose peers never arrive gives up after a few seconds (bounded wait): the call still
+ * returns CATS_OK (it is asynchronous) and cats_read_counters reports a non-zero device status.
+ * CATS_ERR_MODE: the shape cannot run as one persistent kernel with one CTA per SM on this GPU
+ * (then use one all-reduce per layer around cats_mlp instead).  nranks == 1 is allowed (the
+ * exchange then runs against the caller's own buffer).
+ * No reference counterpart: the reference has no tensor parallelism (its multi-GPU inference
+ * mode is layer placement, experiments/bench_sparse_inference_llama.py:36).
+ */
+size_t cats_tp_exchange_bytes(int H);
+int cats_tp_exchange_alloc(int H, void** ptr, unsigned char* handle64);
+int cats_tp_exchange_open(const unsigned char* handle64, void** ptr);
+int cats_tp_exchange_close(void* ptr);
+int cats_tp_exchange_free(void* ptr);
+int cats_tp_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const void* const* WdT,
+                      const float* thresholds, void* x_io, void* resid, void* ws, size_t ws_bytes,
+                      int B, int H, int I_local, int dtype, float eps, int nranks, int rank,
+                      void* const* exchange, void* stream);
+
+/*
  * 1 if cats_mlp_stack runs these L layers as ONE persistent cooperative launch on the current
  * device (shape, batch and options permitting), 0 if it launches two kernels per layer.
  * For reporting (benchmarks count their kernel launches with it).  No reference counterpart.
