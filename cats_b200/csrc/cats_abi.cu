@@ -177,6 +177,7 @@ struct Options {
   int use_tma = 1;     // TMA-fed kernels where the shape allows (else the direct-load kernels)
   int ring_kb = 200;   // shared-memory ring per TMA kernel
   int use_mega = 1;    // persistent cooperative kernel for cats_mlp / cats_mlp_stack
+  int bulk_flush = 1;  // persistent kernel: flush accumulators with TMA bulk reduces
 };
 Options& options() {
   static Options o = [] {
@@ -185,6 +186,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_RING_KB")) v.ring_kb = atoi(e);
     if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
     if (const char* e = getenv("CATS_B200_MEGA")) v.use_mega = atoi(e);
+    if (const char* e = getenv("CATS_B200_BULK_FLUSH")) v.bulk_flush = atoi(e);
     return v;
   }();
   return o;
@@ -317,7 +319,7 @@ cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, cons
 // ---- persistent kernel ------------------------------------------------------------------------
 struct MegaPlan {
   bool ok = false;
-  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0;
+  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0, bulk_flush = 0;
   size_t smem = 0;
 };
 
@@ -340,9 +342,13 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   p.rmax = (half_rows + p.grid - 1) / p.grid + 1;
   p.cap = p.rmax;
   const int bt = batch_tile(B);
+  // staging area of the bulk-reduce flush: 32 vectors of fp32 per consumer warp (needs whole
+  // warps of vectors: H a multiple of 32 vectors)
+  p.bulk_flush = (o.bulk_flush && nvec % 32 == 0) ? 1 : 0;
+  const size_t stage = p.bulk_flush ? 128 + (size_t)kConsumerWarps * 32 * vecn(dtype) * sizeof(float) : 0;
   const size_t fixed = 16 + (size_t)B * row_bytes * (has_resid ? 2 : 1) +
                        kParts * (sizeof(float) * (size_t)p.rmax * bt + sizeof(int) * (size_t)p.cap +
-                                 sizeof(float) * (size_t)p.cap * bt);
+                                 sizeof(float) * (size_t)p.cap * bt) + stage;
   const size_t limit = (size_t)dev_info().max_smem_optin;
   const size_t statics = 2048;  // static shared memory of the kernel + slack
   if (limit < fixed + statics + 2 * row_bytes + 1024) return p;
@@ -427,6 +433,7 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   A.S = p.S;
   A.cw = p.cw;
   A.npw = (p.S % kMegaProducers == 0) ? kMegaProducers : 2;
+  A.bulk_flush = p.bulk_flush;
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
   A.cap = p.cap;
   A.rmax = p.rmax;
@@ -513,6 +520,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "ring_kb")) options().ring_kb = value;
   else if (!strcmp(name, "pdl")) g_use_pdl = value;
   else if (!strcmp(name, "mega")) options().use_mega = value;
+  else if (!strcmp(name, "bulk_flush")) options().bulk_flush = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }

@@ -70,6 +70,7 @@ struct MegaArgs {
   int L, B, H, I;
   int S, cw, cap, rmax;  // ring stages, dot-owner warps (divides S), list capacity, rows/segment
   int npw;               // producer threads in use (divides S)
+  int bulk_flush;        // 1: accumulators leave through shared memory and TMA bulk reduces
   unsigned s_magic;      // floor(2^32 / S) + 1: item -> (ring cycle, slot) without a division
   float eps;
   const void* x_in;  // [B,H] input of layer 0
@@ -202,6 +203,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   int* s_idx = reinterpret_cast<int*>(smem + off);  // [kParts][cap]
   off += kParts * sizeof(int) * (size_t)A.cap;
   float* s_hg = reinterpret_cast<float*>(smem + off);  // [kParts][cap * BT]
+  off += kParts * sizeof(float) * (size_t)A.cap * BT;
+  off = align_up(off, 128);
+  float* s_flush = reinterpret_cast<float*>(smem + off);  // [kConsumerWarps][32 * N] if bulk_flush
 
   const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(bars), empty_u = full_u + 8u * S;
   const uint32_t lready_u = empty_u + 8u * S, lfree_u = lready_u + 8u * kParts,
@@ -492,6 +496,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (tid == 0 && ok) grid_wait(obar, otarget(l), &s_abort);
       }
       consumer_bar_sync();
+      CATS_STAMP(0, 4, (l + 1 == L / 2) && tid == 0);
       ok = !s_abort;
       const float* accp = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H)
                             : ws.acc32 + (size_t)(l & 1) * kMaxB * H;
@@ -556,6 +561,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
           }
         }
+        CATS_STAMP(0, 5, (l + 1 == L / 2) && tid == 0 && b == 0);
         if (has_resid) {
           ss = warp_sum(ss);
           consumer_bar_sync();
@@ -727,8 +733,45 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (lane == 0 && ok) mbar_arrive(lfree_u + 8u * h);
       }
 
+      CATS_STAMP(0, 15, tl && tid == 0);
       // ---- this CTA's share of the down projection into the layer's fp32 accumulators ----------
-      if (ok) {
+      if (ok && A.bulk_flush) {
+        // Through shared memory: a warp's 32 vectors of one (g, t) are 32 * N contiguous
+        // columns, written to the warp's staging area and added to the accumulators by one
+        // bulk reduce.  The staging area is reused once the previous reduce has read it.
+        float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+        float* stg = s_flush + (size_t)warp * 32 * N;
+        const uint32_t stg_u = smem_u32(stg);
+        bool first = true;
+#pragma unroll
+        for (int g = 0; g < NVT; ++g) {
+          const int v0 = g * kConsumerThreads + warp * 32;  // the warp's first vector
+          if (v0 < nvec) {                                   // nvec is a multiple of 32
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              if (t < B) {
+                if (!first) {
+                  if (lane == 0) bulk_wait_read();
+                  __syncwarp();
+                }
+                first = false;
+#pragma unroll
+                for (int i = 0; i < N; i += 4)
+                  *reinterpret_cast<float4*>(stg + lane * N + i) =
+                      make_float4(acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2], acc[g][t][i + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  bulk_reduce_add_f32(accp + (size_t)t * H + (size_t)v0 * N, stg_u,
+                                      32u * N * (uint32_t)sizeof(float));
+                  bulk_commit();
+                }
+              }
+            }
+          }
+        }
+        if (lane == 0) bulk_wait_all();
+      } else if (ok) {
         float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
 #pragma unroll
         for (int g = 0; g < NVT; ++g) {

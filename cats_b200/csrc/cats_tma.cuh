@@ -115,6 +115,23 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint3
           "r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// Bulk add of `bytes` fp32 values from this CTA's shared memory into global memory (TMA reduce:
+// one request per 128 bytes at L2 instead of one per 16-byte red).  Both addresses 16-byte
+// aligned, bytes a multiple of 16.  The writes to shared memory that filled the source must be
+// followed by fence_proxy_async() before this is issued.
+__device__ __forceinline__ void bulk_reduce_add_f32(float* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile(
+      "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst),
+      "r"(src_smem), "r"(bytes)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the source has been read (it may be overwritten) / the operations are complete
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void consumer_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
