@@ -64,6 +64,10 @@ SIGNATURES = {
                                    _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
                                    _c_int, _c_int, ctypes.c_float, _c_int, _c_int,
                                    ctypes.POINTER(_c_void_p), _c_void_p]),
+    "cats_histogram": (_c_int, [_c_void_p, _c_size_t, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
+                                _c_void_p]),
+    "cats_histogram_threshold": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_float, _c_void_p,
+                                          _c_void_p]),
     "cats_uses_persistent_kernel": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int]),
     "cats_down_dense": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                  _c_void_p]),

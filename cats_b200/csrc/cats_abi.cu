@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "cats_mega.cuh"
+#include "cats_stats.cuh"
 
 namespace {
 
@@ -878,6 +879,39 @@ int cats_transpose(const void* src, void* dst, int rows, int cols, int dtype, vo
     k_transpose<uint32_t><<<grid, block, 0, st>>>((const uint32_t*)src, (uint32_t*)dst, rows, cols);
   else
     k_transpose<uint16_t><<<grid, block, 0, st>>>((const uint16_t*)src, (uint16_t*)dst, rows, cols);
+  return cuda_status(cudaGetLastError());
+}
+
+int cats_histogram(const void* values, size_t n, int dtype, const float* edges, int n_edges,
+                   unsigned long long* counts, int take_abs, void* stream) {
+  if (dtype != CATS_F32 && dtype != CATS_F16 && dtype != CATS_BF16) return CATS_ERR_DTYPE;
+  if (n_edges < 2 || n_edges > kHistMaxEdges) return CATS_ERR_SHAPE;
+  if (!edges || !counts || (!values && n)) return CATS_ERR_NULL;
+  if (((uintptr_t)values) % esize(dtype)) return CATS_ERR_ALIGN;
+  if (n == 0) return CATS_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int threads = kHistWarps * 32;
+  const size_t per_block = (size_t)threads * 16 / esize(dtype) * 4;  // 4 vectors per thread
+  size_t blocks = (n + per_block - 1) / per_block;
+  const size_t cap = (size_t)dev_info().sms * 4;
+  if (blocks > cap) blocks = cap;
+  const dim3 grid((unsigned)blocks), block(threads);
+  if (dtype == CATS_F32)
+    k_histogram<float><<<grid, block, 0, st>>>((const float*)values, n, edges, n_edges, counts, take_abs);
+  else if (dtype == CATS_F16)
+    k_histogram<__half><<<grid, block, 0, st>>>((const __half*)values, n, edges, n_edges, counts, take_abs);
+  else
+    k_histogram<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)values, n, edges, n_edges,
+                                                       counts, take_abs);
+  return cuda_status(cudaGetLastError());
+}
+
+int cats_histogram_threshold(const unsigned long long* counts, const float* edges, int n_edges,
+                             float sparsity, float* threshold, void* stream) {
+  if (n_edges < 2 || n_edges > kHistMaxEdges) return CATS_ERR_SHAPE;
+  if (!counts || !edges || !threshold) return CATS_ERR_NULL;
+  k_hist_threshold<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, edges, n_edges, sparsity,
+                                                                    threshold);
   return cuda_status(cudaGetLastError());
 }
 

@@ -341,6 +341,46 @@ def transpose(src: torch.Tensor) -> torch.Tensor:
     return dst
 
 
+def histogram(values: torch.Tensor, edges: torch.Tensor, counts: Optional[torch.Tensor] = None,
+              take_abs: bool = False) -> torch.Tensor:
+    """``counts += torch.histogram(values [abs], bins=edges)`` on the device (``cats_histogram``).
+
+    ``edges``: ascending float32 CUDA tensor (the reference's -inf, linspace(-1, 1, 998), +inf);
+    ``counts``: int64 CUDA tensor of len(edges) - 1, created (zero) when omitted.  Replaces the
+    host-side torch.histogram calls of collect_stats (ugly_utils.py:514-522)."""
+    _req(values, "values")
+    dev = values.device
+    if edges.dtype != torch.float32 or edges.device != dev or not edges.is_contiguous() or edges.dim() != 1:
+        raise RuntimeError("cats_b200: histogram edges must be a contiguous 1-D float32 tensor on the values' device")
+    if counts is None:
+        counts = torch.zeros(edges.numel() - 1, dtype=torch.int64, device=dev)
+    if counts.dtype != torch.int64 or counts.device != dev or not counts.is_contiguous() \
+            or counts.numel() != edges.numel() - 1:
+        raise RuntimeError("cats_b200: histogram counts must be int64[len(edges) - 1] on the values' device")
+    with _on(dev):
+        _lib.check(_lib.lib().cats_histogram(values.data_ptr(), values.numel(), dtype_code(values.dtype),
+                                             edges.data_ptr(), edges.numel(), counts.data_ptr(),
+                                             1 if take_abs else 0, _stream(dev)), "cats_histogram")
+    return counts
+
+
+def histogram_threshold(counts: torch.Tensor, edges: torch.Tensor, sparsity: float) -> torch.Tensor:
+    """0-dim float32 CUDA tensor: the bin edge at which the histogram's CDF crosses ``sparsity``
+    (``cats_histogram_threshold``; get_threshold, ugly_utils.py:236-245, without leaving the device)."""
+    dev = counts.device
+    if counts.dtype != torch.int64 or not counts.is_cuda or not counts.is_contiguous():
+        raise RuntimeError("cats_b200: histogram counts must be a contiguous int64 CUDA tensor")
+    if edges.dtype != torch.float32 or edges.device != dev or edges.numel() != counts.numel() + 1 \
+            or not edges.is_contiguous():
+        raise RuntimeError("cats_b200: need len(counts) + 1 float32 edges on the same device")
+    out = torch.empty((), dtype=torch.float32, device=dev)
+    with _on(dev):
+        _lib.check(_lib.lib().cats_histogram_threshold(counts.data_ptr(), edges.data_ptr(), edges.numel(),
+                                                       float(sparsity), out.data_ptr(), _stream(dev)),
+                   "cats_histogram_threshold")
+    return out
+
+
 # Packed WdT per down_proj weight.  Keyed on storage pointer, shape, dtype and the tensor's
 # in-place version counter, so a weight that is modified or replaced is re-packed.
 _packed = {}

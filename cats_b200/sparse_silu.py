@@ -88,6 +88,7 @@ class CatsSparseSiluMLP(nn.Module):
         num_bins = 1000
         bins = torch.linspace(-1, 1, num_bins - 2)
         self.histogram_bins = torch.cat([torch.tensor([-torch.inf]), bins, torch.tensor([torch.inf])])
+        self._dev_hist = {}     # device -> (edges, pre counts, post counts): int64, on that device
         self.pre_act_hist_counts = torch.zeros(num_bins - 1)
         self.abs_post_act_hist_counts = torch.zeros(num_bins - 1)
         self.post_act_hist_counts = torch.zeros(num_bins - 1)
@@ -97,7 +98,37 @@ class CatsSparseSiluMLP(nn.Module):
 
         self.sparse_act_fn = SparseSiLU(threshold=self.dead_threshold)
 
-    # ---- statistics (host-side, as in the reference) ----------------------------------------
+    # ---- statistics ---------------------------------------------------------------------------
+    # The reference keeps the two histograms as float32 CPU tensors and fills them with
+    # torch.histogram after copying the activations to the host on every forward
+    # (ugly_utils.py:514-522).  Here CUDA activations are binned where they are (cats_histogram,
+    # exact 64-bit counts per device); the counts are folded into the float32 CPU tensors of the
+    # reference's format whenever those are read.
+    def _fold_device_counts(self):
+        for dev, (edges, pre, post) in list(self.__dict__.get("_dev_hist", {}).items()):
+            self._pre_counts += pre.cpu().to(torch.float32)
+            self._post_counts += post.cpu().to(torch.float32)
+            pre.zero_()
+            post.zero_()
+
+    @property
+    def pre_act_hist_counts(self):
+        self._fold_device_counts()
+        return self._pre_counts
+
+    @pre_act_hist_counts.setter
+    def pre_act_hist_counts(self, value):
+        self._pre_counts = value
+
+    @property
+    def post_act_hist_counts(self):
+        self._fold_device_counts()
+        return self._post_counts
+
+    @post_act_hist_counts.setter
+    def post_act_hist_counts(self, value):
+        self._post_counts = value
+
     def activate_stats(self, is_collect_histogram: bool = True):
         self.is_stats = True
         self.dead_percentage = 0
@@ -109,6 +140,17 @@ class CatsSparseSiluMLP(nn.Module):
         self.is_stats = False
 
     def collect_stats(self, pre_activation, post_activation):
+        if pre_activation.is_cuda and post_activation.is_cuda:
+            dev = pre_activation.device
+            if dev not in self._dev_hist:
+                n = self.histogram_bins.numel() - 1
+                self._dev_hist[dev] = (self.histogram_bins.to(dev, torch.float32).contiguous(),
+                                       torch.zeros(n, dtype=torch.int64, device=dev),
+                                       torch.zeros(n, dtype=torch.int64, device=dev))
+            edges, pre_counts, post_counts = self._dev_hist[dev]
+            ops.histogram(pre_activation.detach().contiguous(), edges, pre_counts)
+            ops.histogram(post_activation.detach().contiguous(), edges, post_counts, take_abs=True)
+            return
         pre_activation = pre_activation.float().cpu().detach()
         post_activation = post_activation.float().cpu().detach()
         self.pre_act_hist_counts += torch.histogram(pre_activation, bins=self.histogram_bins)[0]

@@ -243,6 +243,29 @@ int cats_tp_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const
 int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype);
 
 /*
+ * Activation histogram on the device: counts[b] += |{ i : edges[b] <= v_i < edges[b+1] }| for the
+ * n values at `values` (element type dtype), the last bin closed on the right and values outside
+ * [edges[0], edges[n_edges-1]] (and NaNs) ignored: torch.histogram's rule.  take_abs != 0 bins
+ * |v_i|.  edges: n_edges <= 1024 ascending fp32 values in device memory (+-inf allowed at the
+ * ends); counts: n_edges - 1 64-bit counters in device memory, accumulated into (the caller
+ * zeroes them once).  Replaces the two torch.histogram calls of collect_stats
+ * (experiments/models/sparse_silu/ugly_utils.py:514-522), which first copy both activation
+ * tensors to the host: pre-activations with take_abs = 0, post-activations with take_abs = 1,
+ * edges = -inf, linspace(-1, 1, 998), +inf (ugly_utils.py:491-493).
+ */
+int cats_histogram(const void* values, size_t n, int dtype, const float* edges, int n_edges,
+                   unsigned long long* counts, int take_abs, void* stream);
+
+/*
+ * *threshold (device memory) = edges[first b with cdf(b) > sparsity], cdf = running sum of
+ * counts / total; edges[n_edges - 1] if the CDF never exceeds it.  Same arithmetic as
+ * get_threshold (ugly_utils.py:236-245: float32 probabilities, torch.cumsum, searchsorted
+ * side="right") for totals below 2^24, where float32 counts are still exact.
+ */
+int cats_histogram_threshold(const unsigned long long* counts, const float* edges, int n_edges,
+                             float sparsity, float* threshold, void* stream);
+
+/*
  * Dense down projection over Wd [H, I] (nn.Linear layout): out[b,h] = sum_i Wd[h,i] * inter[b,i].
  * Reads all of Wd whatever the sparsity; exists for callers that cannot supply WdT.
  * Replaces gemv_local_kernel (fuse_gemv_cmp_cuda.cu:1786-1960).

@@ -90,12 +90,15 @@ def union_mask(mask: np.ndarray) -> np.ndarray:
 
 
 def get_threshold(bin_edges, histogram_counts, sparsity_level):
-    """ugly_utils.py:236-245: normalise, cumsum, searchsorted(side='right'), take that edge.
-    Arithmetic in float32 like the reference's tensors."""
-    counts = np.asarray(histogram_counts, dtype=np.float32)
-    counts = counts / counts.sum(dtype=np.float32)
-    cdf = np.cumsum(counts, dtype=np.float32)
-    idx = int(np.searchsorted(cdf, np.float32(sparsity_level), side="right"))
+    """ugly_utils.py:236-245: normalise, cumsum, searchsorted(side='right'), take that edge —
+    with the reference's own torch calls on float32 tensors (torch's CPU cumsum keeps its running
+    sum in double and rounds every element to float32; a float32 running sum can land one bin
+    away when the CDF passes within an ulp of the sparsity level)."""
+    import torch
+
+    counts = torch.as_tensor(np.asarray(histogram_counts, dtype=np.float32)).clone()
+    counts /= counts.sum()
+    idx = int(torch.searchsorted(counts.cumsum(0), float(sparsity_level), side="right"))
     return np.asarray(bin_edges)[idx]
 
 
@@ -170,3 +173,24 @@ def torch_dense_masked_mlp(x, wg, wu, wd, threshold):
     dead_neurons = post_act.abs() <= threshold
     post_act[dead_neurons] = 0
     return F.linear(post_act * F.linear(x, wu), wd)
+
+
+def activation_histograms(pre_activation, post_activation, bins):
+    """The two histograms of collect_stats (ugly_utils.py:514-522): torch.histogram of the
+    pre-activations and of |post-activations| over ``bins`` (float32 edges).  Returns int64
+    numpy arrays (pre_counts, post_counts)."""
+    import torch
+
+    pre = torch.as_tensor(np.asarray(pre_activation, dtype=np.float32)).flatten()
+    post = torch.as_tensor(np.asarray(post_activation, dtype=np.float32)).flatten()
+    edges = torch.as_tensor(np.asarray(bins, dtype=np.float32))
+    return (torch.histogram(pre, bins=edges)[0].numpy().astype(np.int64),
+            torch.histogram(torch.abs(post), bins=edges)[0].numpy().astype(np.int64))
+
+
+def reference_bins(num_bins=1000):
+    """-inf, 998 points on [-1, 1], +inf (ugly_utils.py:491-493)."""
+    import torch
+
+    b = torch.linspace(-1, 1, num_bins - 2)
+    return torch.cat([torch.tensor([-torch.inf]), b, torch.tensor([torch.inf])]).numpy()

@@ -112,3 +112,12 @@ def test_mlp_stack_is_chain_of_layers():
         rr = rr + O.dense_masked_mlp(xr, wg, wu, wd, 0.1)["out"]
         xr = O.rmsnorm(rr)
     assert np.allclose(x, xr) and np.allclose(r, rr) and len(counts) == 3
+
+
+def test_activation_histograms_match_the_reference_collect_stats():
+    """The oracle's histograms against the counts the reference's own collect_stats produced."""
+    g = load_golden("get_threshold_0")
+    pre, post = O.activation_histograms(g["pre"], g["post"], g["bins"])
+    assert np.array_equal(pre, g["pre_counts"].astype(np.int64))
+    assert np.array_equal(post, g["counts"].astype(np.int64))
+    assert np.array_equal(O.reference_bins().astype(np.float64), g["bins"])
