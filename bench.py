@@ -454,6 +454,25 @@ def run_gpu_arm(args):
         "staged_kernels": staged, "n_active_mean": n_act, "intermediate_local": I_local,
     }
 
+    # ---- statistics kernel beside the path (threshold calibration): HBM-bound stream ----------
+    stats = None
+    if world == 1 and not args.no_dense:
+        nval = 160 * 1000 * 1000                       # 320 MB of fp16 activations: larger than L2
+        vals = torch.nn.functional.silu(torch.randn(nval // 8, device=dev) * 1.28).to(dtype).repeat(8)
+        edges = torch.cat([torch.tensor([-torch.inf]), torch.linspace(-1, 1, 998),
+                           torch.tensor([torch.inf])]).to(dev)
+        hcounts = torch.zeros(999, dtype=torch.int64, device=dev)
+        for _ in range(2):
+            ops.histogram(vals, edges, hcounts, take_abs=True)
+        h_us = per_launch_us(lambda i: ops.histogram(vals, edges, hcounts, take_abs=True), 1, 5, stream)
+        hb = vals.numel() * vals.element_size()
+        stats = {"k_histogram": {"us": h_us[1], "bytes": hb, "GBps": hb / h_us[1] / 1e3,
+                                 "frac": hb / h_us[1] / 1e3 / peak,
+                                 "bound": "instruction issue (about 20 instructions per value), not HBM",
+                                 "what": f"|post-activation| histogram of {vals.numel()} {dtype} values "
+                                         "(SiLU of N(0, 1.28^2)), the reference's 999 bins"}}
+        del vals
+
     # ---- dense cuBLAS MLP of the same shape (context; single GPU only) -----------------------
     dense = None
     if world == 1 and not args.no_dense:
@@ -523,6 +542,8 @@ def run_gpu_arm(args):
         "roofline": roofline, "clocks": clocks.summary(), "dense_cublas": dense,
         "cpu_baseline": cpu,
     }
+    if stats is not None:
+        line["roofline"]["stats_kernels"] = stats
     if world > 1:
         line["tp"] = {"mode": tp_mode, "nccl_allreduce_variant": nccl_variant}
     print(json.dumps(line), flush=True)

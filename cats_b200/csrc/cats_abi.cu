@@ -355,19 +355,29 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   if (limit < fixed + statics + 2 * row_bytes + 1024) return p;
   int smax = (int)((limit - fixed - statics - 1024) / (row_bytes + 16));
   if (smax > 48) smax = 48;
-  // even stage count (two producers), as many dot-owner warps (a divisor <= 8) as possible
-  for (int cand = smax; cand >= 2 && cand >= smax - 5; --cand) {
+  // Stage count: even (at least two producer threads), preferring, in this order, as many
+  // dot-owner warps as possible (a divisor of S, at most 8), four producer threads (S a
+  // multiple of 4; with two the copies are issued too slowly) and depth.
+  for (int cand = smax; cand >= 2 && cand >= smax - 7; --cand) {
     if (cand & 1) continue;
     int cw = 1;
     for (int d = 1; d <= kConsumerWarps; ++d)
       if (cand % d == 0) cw = d;
-    if (cw > p.cw || p.S == 0) {
-      if (p.S == 0 || cw > p.cw) {
-        p.cw = cw;
-        p.S = cand;
-      }
+    const int four = (cand % kMegaProducers == 0) ? 1 : 0;
+    const int best_four = (p.S % kMegaProducers == 0) ? 1 : 0;
+    if (p.S == 0 || cw > p.cw || (cw == p.cw && four > best_four)) {
+      p.cw = cw;
+      p.S = cand;
     }
   }
+#ifdef CATS_PHASE_TIMING
+  if (const char* e = getenv("CATS_DEV_S")) {  // development: force the stage count
+    p.S = atoi(e);
+    p.cw = 1;
+    for (int d = 1; d <= kConsumerWarps; ++d)
+      if (p.S % d == 0) p.cw = d;
+  }
+#endif
   if (p.S < 2) return p;
   p.smem = align_up((size_t)p.S * row_bytes + 8 * (size_t)(2 * p.S + 3 * kParts + 1), 16) + fixed;
   p.ok = p.smem + statics <= limit;
@@ -890,19 +900,25 @@ int cats_histogram(const void* values, size_t n, int dtype, const float* edges, 
   if (((uintptr_t)values) % esize(dtype)) return CATS_ERR_ALIGN;
   if (n == 0) return CATS_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int threads = kHistWarps * 32;
-  const size_t per_block = (size_t)threads * 16 / esize(dtype) * 4;  // 4 vectors per thread
+  const size_t smem = hist_smem_bytes(n_edges);
+  const size_t per_block = (size_t)kHistThreads * 16 / esize(dtype) * 2;  // 2 vectors per thread
   size_t blocks = (n + per_block - 1) / per_block;
-  const size_t cap = (size_t)dev_info().sms * 4;
-  if (blocks > cap) blocks = cap;
-  const dim3 grid((unsigned)blocks), block(threads);
-  if (dtype == CATS_F32)
-    k_histogram<float><<<grid, block, 0, st>>>((const float*)values, n, edges, n_edges, counts, take_abs);
-  else if (dtype == CATS_F16)
-    k_histogram<__half><<<grid, block, 0, st>>>((const __half*)values, n, edges, n_edges, counts, take_abs);
-  else
-    k_histogram<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)values, n, edges, n_edges,
-                                                       counts, take_abs);
+  if (blocks > (size_t)dev_info().sms) blocks = (size_t)dev_info().sms;  // one CTA per SM
+  const dim3 grid((unsigned)blocks), block(kHistThreads);
+  cudaError_t e;
+#define CATS_HIST_LAUNCH(T)                                                                      \
+  do {                                                                                           \
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k_histogram<T>),                      \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    if (e == cudaSuccess)                                                                        \
+      k_histogram<T><<<grid, block, smem, st>>>((const T*)values, n, edges, n_edges, counts,     \
+                                                take_abs);                                       \
+  } while (0)
+  if (dtype == CATS_F32) CATS_HIST_LAUNCH(float);
+  else if (dtype == CATS_F16) CATS_HIST_LAUNCH(__half);
+  else CATS_HIST_LAUNCH(__nv_bfloat16);
+#undef CATS_HIST_LAUNCH
+  if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(cudaGetLastError());
 }
 
