@@ -179,6 +179,7 @@ struct Options {
   int ring_kb = 200;   // shared-memory ring per TMA kernel
   int use_mega = 1;    // persistent cooperative kernel for cats_mlp / cats_mlp_stack
   int bulk_flush = 1;  // persistent kernel: flush accumulators with TMA bulk reduces
+  int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
 };
 Options& options() {
   static Options o = [] {
@@ -188,6 +189,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
     if (const char* e = getenv("CATS_B200_MEGA")) v.use_mega = atoi(e);
     if (const char* e = getenv("CATS_B200_BULK_FLUSH")) v.bulk_flush = atoi(e);
+    if (const char* e = getenv("CATS_B200_MMA_DOT")) v.mma_dot = atoi(e);
     return v;
   }();
   return o;
@@ -320,7 +322,7 @@ cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, cons
 // ---- persistent kernel ------------------------------------------------------------------------
 struct MegaPlan {
   bool ok = false;
-  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0, bulk_flush = 0;
+  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0, bulk_flush = 0, mma_dot = 0;
   size_t smem = 0;
 };
 
@@ -346,14 +348,20 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   // staging area of the bulk-reduce flush: 32 vectors of fp32 per consumer warp (needs whole
   // warps of vectors: H a multiple of 32 vectors)
   p.bulk_flush = (o.bulk_flush && nvec % 32 == 0) ? 1 : 0;
-  const size_t stage = p.bulk_flush ? 128 + (size_t)kConsumerWarps * 32 * vecn(dtype) * sizeof(float) : 0;
-  const size_t fixed = 16 + (size_t)B * row_bytes * (has_resid ? 2 : 1) +
+  // tensor-core dot products: 16-bit weights, every warp's column range a whole number of
+  // double steps (32 columns), partial sums of two groups in shared memory
+  // (batches only: for one token the warp-per-row FMA path keeps up with HBM and needs no
+  // barrier per group)
+  p.mma_dot = (o.mma_dot && B >= 2 && dtype != CATS_F32 && H % (32 * kConsumerWarps) == 0) ? 1 : 0;
+  const size_t stage = (p.bulk_flush ? 128 + (size_t)kConsumerWarps * 32 * vecn(dtype) * sizeof(float) : 0) +
+                       (p.mma_dot ? sizeof(float) * 2 * kConsumerWarps * 8 * bt : 0);
+  const size_t fixed = 16 + (size_t)B * (row_bytes + 16) + (has_resid ? (size_t)B * row_bytes : 0) +
                        kParts * (sizeof(float) * (size_t)p.rmax * bt + sizeof(int) * (size_t)p.cap +
                                  sizeof(float) * (size_t)p.cap * bt) + stage;
   const size_t limit = (size_t)dev_info().max_smem_optin;
   const size_t statics = 2048;  // static shared memory of the kernel + slack
   if (limit < fixed + statics + 2 * row_bytes + 1024) return p;
-  int smax = (int)((limit - fixed - statics - 1024) / (row_bytes + 16));
+  int smax = (int)((limit - fixed - statics - 1024) / (row_bytes + 16 + 16));
   if (smax > 48) smax = 48;
   // Stage count: even (at least two producer threads), preferring, in this order, as many
   // dot-owner warps as possible (a divisor of S, at most 8), four producer threads (S a
@@ -379,7 +387,8 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   }
 #endif
   if (p.S < 2) return p;
-  p.smem = align_up((size_t)p.S * row_bytes + 8 * (size_t)(2 * p.S + 3 * kParts + 1), 16) + fixed;
+  if (p.S < 8) p.mma_dot = 0;  // a group of eight rows has to fit in the ring
+  p.smem = align_up((size_t)p.S * (row_bytes + 16) + 8 * (size_t)(2 * p.S + 3 * kParts + 1), 16) + fixed;
   p.ok = p.smem + statics <= limit;
   return p;
 }
@@ -445,6 +454,7 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   A.cw = p.cw;
   A.npw = (p.S % kMegaProducers == 0) ? kMegaProducers : 2;
   A.bulk_flush = p.bulk_flush;
+  A.mma_dot = p.mma_dot;
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
   A.cap = p.cap;
   A.rmax = p.rmax;
@@ -532,6 +542,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "pdl")) g_use_pdl = value;
   else if (!strcmp(name, "mega")) options().use_mega = value;
   else if (!strcmp(name, "bulk_flush")) options().bulk_flush = value;
+  else if (!strcmp(name, "mma_dot")) options().mma_dot = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }

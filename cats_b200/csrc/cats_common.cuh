@@ -188,6 +188,22 @@ struct VecT<__half> {
           : "r"(wv[i]), "r"(h));
     }
   }
+  // axpy with the scalar rounded to the storage type (what the reference's stage 2 hands to its
+  // stage 3: flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu keeps gate*up in the weights' dtype):
+  // one mixed-precision FMA per weight.  Used for batches, where the FMA count is the limit.
+  static __device__ __forceinline__ uint32_t prep1(float h) {
+    return (uint32_t)__half_as_ushort(__float2half_rn(h));
+  }
+  static __device__ __forceinline__ void axpy1(uint32_t h, const uint4& w, float* acc) {
+    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      asm("{\n\t.reg .b16 wl, wh, hh, hx;\n\tmov.b32 {wl, wh}, %2;\n\tmov.b32 {hh, hx}, %3;\n\t"
+          "fma.rn.f32.f16 %0, wl, hh, %0;\n\tfma.rn.f32.f16 %1, wh, hh, %1;\n\t}"
+          : "+f"(acc[2 * i]), "+f"(acc[2 * i + 1])
+          : "r"(wv[i]), "r"(h));
+    }
+  }
 };
 
 template <>
@@ -231,6 +247,19 @@ struct VecT<__nv_bfloat16> {
     unpack(w, fw);
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = fmaf(h, fw[i], acc[i]);
+  }
+  static __device__ __forceinline__ uint32_t prep1(float h) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(h));
+  }
+  static __device__ __forceinline__ void axpy1(uint32_t h, const uint4& w, float* acc) {
+    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      asm("{\n\t.reg .b16 wl, wh, hh, hx;\n\tmov.b32 {wl, wh}, %2;\n\tmov.b32 {hh, hx}, %3;\n\t"
+          "fma.rn.f32.bf16 %0, wl, hh, %0;\n\tfma.rn.f32.bf16 %1, wh, hh, %1;\n\t}"
+          : "+f"(acc[2 * i]), "+f"(acc[2 * i + 1])
+          : "r"(wv[i]), "r"(h));
+    }
   }
 };
 

@@ -34,6 +34,8 @@
 // run into their own limits and leave as well.
 #pragma once
 
+#include <type_traits>
+
 #include "cats_tma.cuh"
 
 namespace cats {
@@ -71,6 +73,7 @@ struct MegaArgs {
   int S, cw, cap, rmax;  // ring stages, dot-owner warps (divides S), list capacity, rows/segment
   int npw;               // producer threads in use (divides S)
   int bulk_flush;        // 1: accumulators leave through shared memory and TMA bulk reduces
+  int mma_dot;           // 1: gate / up dot products of eight rows at a time on the tensor cores
   unsigned s_magic;      // floor(2^32 / S) + 1: item -> (ring cycle, slot) without a division
   float eps;
   const void* x_in;  // [B,H] input of layer 0
@@ -189,13 +192,18 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   auto slot_of = [&](int kk) { return kk - cyc_of(kk) * S; };
 
   // ---- shared memory carve-up -----------------------------------------------------------------
+  // Ring stages and the tokens' x are 16 bytes further apart than a row is long: eight rows
+  // (or tokens) read at the same column then fall into eight different bank groups, which is
+  // what ldmatrix and the B-fragment loads of the tensor-core dot products need.
+  const uint32_t row_stride = row_bytes + 16;
+  const int xs_ld = H + 16 / (int)sizeof(T);
   unsigned char* ring = smem;
-  size_t off = (size_t)S * row_bytes;
+  size_t off = (size_t)S * row_stride;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off);
   off += 8 * (size_t)(2 * S + 3 * kParts + 1);
   off = align_up(off, 16);
   T* xs = reinterpret_cast<T*>(smem + off);
-  off += (size_t)B * row_bytes;
+  off += (size_t)B * row_stride;
   T* rs = reinterpret_cast<T*>(smem + off);
   off += has_resid ? (size_t)B * row_bytes : 0;
   float* s_val = reinterpret_cast<float*>(smem + off);  // [kParts][rmax * BT]
@@ -206,6 +214,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   off += kParts * sizeof(float) * (size_t)A.cap * BT;
   off = align_up(off, 128);
   float* s_flush = reinterpret_cast<float*>(smem + off);  // [kConsumerWarps][32 * N] if bulk_flush
+  off += A.bulk_flush ? sizeof(float) * kConsumerWarps * 32 * N : 0;
+  float* s_part = reinterpret_cast<float*>(smem + off);   // [2][kConsumerWarps][8][BT] if mma_dot
 
   const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(bars), empty_u = full_u + 8u * S;
   const uint32_t lready_u = empty_u + 8u * S, lfree_u = lready_u + 8u * kParts,
@@ -246,7 +256,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     s_abort = 0;
     mbar_fence_init();
   }
-  stage_x<T>(reinterpret_cast<const T*>(A.x_in), xs, B, H);
+  for (int b = 0; b < B; ++b)
+    stage_x<T>(reinterpret_cast<const T*>(A.x_in) + (size_t)b * H, xs + (size_t)b * xs_ld, 1, H);
   if (has_resid) stage_x<T>(reinterpret_cast<const T*>(A.resid), rs, B, H);
   __syncthreads();
 
@@ -274,7 +285,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           return;
         }
         mbar_expect_tx(full_u + 8u * s, row_bytes);
-        tma_load_1d(ring_u + s * row_bytes, src, row_bytes, full_u + 8u * s);
+        tma_load_1d(ring_u + s * row_stride, src, row_bytes, full_u + 8u * s);
       };
       for (int l = 0; l < L && ok; ++l) {
         const bool tl = (l == L / 2) && p == 0;
@@ -578,13 +589,66 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
               const size_t e = (size_t)b * H + 4 * (size_t)g + i;
               T y = V::from_f(V::to_f(rs[e]) * rsq);
               if (nw) y = V::from_f(V::to_f(nw[4 * g + i]) * V::to_f(y));
-              xs[e] = y;
+              xs[(size_t)b * xs_ld + 4 * g + i] = y;
               if (mine && A.x_out) reinterpret_cast<T*>(A.x_out)[e] = y;
             }
           }
         }
       }
       consumer_bar_sync();
+    };
+
+    // Tensor-core dot products (16-bit weights): all consumer warps work on the same group of up
+    // to eight ring rows, warp w on columns [w * H/8, (w+1) * H/8).  Lane q waits for the q-th
+    // row; per 16 columns one ldmatrix fetches the rows' fragments, two 32-bit loads the tokens'
+    // (lanes whose token does not exist keep zeros), one mma adds 8 x 8 partial dots; two
+    // independent accumulator sets hide the mma latency.  Then lane q releases the q-th stage
+    // and the warp leaves its partial sums in `part` ([warp][row][token]) for the caller to add
+    // up after a consumer barrier.  Returns false (warp-uniform) when a wait gave up.
+    const bool mma_dot = A.mma_dot != 0;
+    int dot_groups = 0;  // selects the half of s_part in use
+    auto dot8 = [&](int k0, int nb, float* part) -> bool {
+      bool mine = true;
+      if (lane < nb) {
+        const int kk = k0 + lane, cy = cyc_of(kk);
+        mine = mbar_wait(full_u + 8u * (kk - cy * S), cy & 1, &s_abort);
+      }
+      if (!__all_sync(0xffffffffu, mine)) return false;
+      const int q = lane & 7;
+      const uint32_t rbase = ring_u + (uint32_t)slot_of(k0 + (q < nb ? q : 0)) * row_stride +
+                             ((lane >> 3) & 1) * 16u;
+      const int g = lane >> 2, tq = lane & 3;
+      const T* xp = xs + (size_t)(g < B ? g : 0) * xs_ld + tq * 2;
+      const bool tok = g < B;
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+      const int kw = H / kConsumerWarps;
+      for (int kc = warp * kw; kc < (warp + 1) * kw; kc += 32) {
+        uint32_t a0, a2, a0b, a2b;
+        ldmatrix_x2(rbase + (uint32_t)kc * (uint32_t)sizeof(T), a0, a2);
+        ldmatrix_x2(rbase + (uint32_t)(kc + 16) * (uint32_t)sizeof(T), a0b, a2b);
+        uint32_t b0 = 0u, b1 = 0u, b0b = 0u, b1b = 0u;
+        if (tok) {
+          b0 = *reinterpret_cast<const uint32_t*>(xp + kc);
+          b1 = *reinterpret_cast<const uint32_t*>(xp + kc + 8);
+          b0b = *reinterpret_cast<const uint32_t*>(xp + kc + 16);
+          b1b = *reinterpret_cast<const uint32_t*>(xp + kc + 24);
+        }
+        Mma8<T>::run(d0, a0, a2, b0, b1);
+        Mma8<T>::run(d1, a0b, a2b, b0b, b1b);
+      }
+      __syncwarp();
+      if (lane < nb) mbar_arrive(empty_u + 8u * slot_of(k0 + lane));
+      // this lane holds row g, tokens 2 * tq and 2 * tq + 1
+      if (2 * tq < BT) part[(warp * 8 + g) * BT + 2 * tq] = d0[0] + d1[0];
+      if (2 * tq + 1 < BT) part[(warp * 8 + g) * BT + 2 * tq + 1] = d0[1] + d1[1];
+      return true;
+    };
+    // sum of the eight warps' partial dots of (row, token) = (i / BT, i % BT), for i < 8 * BT
+    auto dot8_sum = [&](const float* part, int i) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) t += part[w * 8 * BT + i];
+      return t;
     };
 
     for (int l = 0; l < L; ++l) {
@@ -604,7 +668,19 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       for (int h = 0; h < kParts; ++h) {
         const int r0 = seg_lo(h), R = seg_hi(h) - r0;
         float* sv = s_val + (size_t)h * A.rmax * BT;
-        if (warp < cw) {
+        if (mma_dot) {
+          // (every warp runs every iteration and every barrier, whatever `ok` is)
+          for (int j0 = 0; j0 < R; j0 += 8) {
+            const int nb = min(8, R - j0);
+            float* part = s_part + (dot_groups++ & 1) * (kConsumerWarps * 8 * BT);
+            if (ok) ok = dot8(k + j0, nb, part);
+            consumer_bar_sync();
+            if (tid < nb * BT && ok) {
+              const float a0 = dot8_sum(part, tid);
+              if (tid % BT < B) sv[j0 * BT + tid] = silu_f(a0);
+            }
+          }
+        } else if (warp < cw) {
           int j = ((warp - k) % cw + cw) % cw;  // first j with (k + j) % cw == warp
           for (; j < R && ok; j += cw) {
             const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
@@ -613,8 +689,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             if (tl && h == 1 && c == 5 && lane == 0 && j < 64) cats_trace[6][j] = cats_now();
 #endif
             float a1[BT];
-            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_bytes), xs, B,
-                                  H, lane, a1);
+            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_stride), xs, B,
+                                  H, lane, a1, xs_ld);
 #pragma unroll
             for (int t = 0; t < BT; ++t) {
               const float a0 = warp_sum(a1[t]);
@@ -638,16 +714,28 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         CATS_STAMP(0, 6 + 4 * h, tl && tid == 0 && h < 2);
         if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
         CATS_STAMP(0, 7 + 4 * h, tl && tid == 0 && h < 2);
+        if (mma_dot) {  // the group loop below needs the same trip count in every warp
+          consumer_bar_sync();
+          ok = !s_abort;
+        }
         const int cnt = ok ? s_cnt[h] : 0;
         float* hg = s_hg + (size_t)h * A.cap * BT;
-        if (warp < cw) {
+        if (mma_dot) {
+          for (int j0 = 0; j0 < cnt; j0 += 8) {
+            const int nb = min(8, cnt - j0);
+            float* part = s_part + (dot_groups++ & 1) * (kConsumerWarps * 8 * BT);
+            if (ok) ok = dot8(k + j0, nb, part);
+            consumer_bar_sync();
+            if (tid < nb * BT && ok) hg[j0 * BT + tid] *= dot8_sum(part, tid);
+          }
+        } else if (warp < cw) {
           int j = ((warp - k) % cw + cw) % cw;
           for (; j < cnt && ok; j += cw) {
             const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
             if (!(ok = mbar_wait_warp(full_u + 8u * s, cy & 1, &s_abort))) break;
             float a1[BT];
-            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_bytes), xs, B,
-                                  H, lane, a1);
+            warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_stride), xs, B,
+                                  H, lane, a1, xs_ld);
 #pragma unroll
             for (int t = 0; t < BT; ++t) {
               const float a0 = warp_sum(a1[t]);
@@ -689,15 +777,19 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
 #endif
           // all loads of a column group first (kDG independent 16-byte loads in flight per
           // thread), then the FMAs: with two warps per scheduler nothing else hides the latency
-          typename V::Scalar hb[kDG][BT];
+          // batches: the scalar rounded to the storage type, one FMA per weight (prep1 / axpy1)
+          constexpr bool kOneFma = BT >= 2 && sizeof(T) == 2;
+          typedef typename std::conditional<kOneFma, uint32_t, typename V::Scalar>::type HScalar;
+          HScalar hb[kDG][BT];
           const uint4* rowp[kDG];
 #pragma unroll
           for (int q = 0; q < kDG; ++q) {
             const int qq = q < nb ? q : 0;
-            rowp[q] = reinterpret_cast<const uint4*>(ring + (size_t)slot_of(k + j0 + qq) * row_bytes);
+            rowp[q] = reinterpret_cast<const uint4*>(ring + (size_t)slot_of(k + j0 + qq) * row_stride);
 #pragma unroll
             for (int t = 0; t < BT; ++t)
-              hb[q][t] = V::prep(q < nb ? hg[(j0 + q) * BT + t] : 0.f);
+              if constexpr (kOneFma) hb[q][t] = V::prep1(q < nb ? hg[(j0 + q) * BT + t] : 0.f);
+              else hb[q][t] = V::prep(q < nb ? hg[(j0 + q) * BT + t] : 0.f);
           }
 #pragma unroll
           for (int g = 0; g < NVT; ++g) {
@@ -709,7 +801,10 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
 #pragma unroll
               for (int q = 0; q < kDG; ++q)
 #pragma unroll
-                for (int t = 0; t < BT; ++t) V::axpy(hb[q][t], wq[q], acc[g][t]);
+                for (int t = 0; t < BT; ++t) {
+                  if constexpr (kOneFma) V::axpy1(hb[q][t], wq[q], acc[g][t]);
+                  else V::axpy(hb[q][t], wq[q], acc[g][t]);
+                }
             }
           }
           __syncwarp();

@@ -203,12 +203,13 @@ __device__ __forceinline__ void warp_dot2_smem(const T* w0, const T* w1, const T
 // shared memory).  Eight vectors are fetched before the first FMA; four partial sums per token.
 template <typename T, int BT>
 __device__ __forceinline__ void warp_dot1_smem(const T* w0, const T* xs, int B, int H, int lane,
-                                               float (&acc)[BT]) {
+                                               float (&acc)[BT], int xs_ld = 0) {
   constexpr int N = VecT<T>::N;
   constexpr int U = 8;
   const int nvec = H / N;
   const uint4* p0 = reinterpret_cast<const uint4*>(w0);
   const uint4* px = reinterpret_cast<const uint4*>(xs);
+  const int xv = (xs_ld ? xs_ld : H) / N;  // 16-byte vectors between the tokens' x
   float part[4][BT];
 #pragma unroll
   for (int q = 0; q < 4; ++q)
@@ -223,17 +224,58 @@ __device__ __forceinline__ void warp_dot1_smem(const T* w0, const T* xs, int B, 
     for (int u = 0; u < U; ++u) {
 #pragma unroll
       for (int t = 0; t < BT; ++t)
-        if (t < B) VecT<T>::fma1(a[u], px[(size_t)t * nvec + v + 32 * u], part[u & 3][t]);
+        if (t < B) VecT<T>::fma1(a[u], px[(size_t)t * xv + v + 32 * u], part[u & 3][t]);
     }
   }
   for (; v < nvec; v += 32) {
     const uint4 a = p0[v];
 #pragma unroll
     for (int t = 0; t < BT; ++t)
-      if (t < B) VecT<T>::fma1(a, px[(size_t)t * nvec + v], part[0][t]);
+      if (t < B) VecT<T>::fma1(a, px[(size_t)t * xv + v], part[0][t]);
   }
 #pragma unroll
   for (int t = 0; t < BT; ++t) acc[t] = (part[0][t] + part[1][t]) + (part[2][t] + part[3][t]);
+}
+
+// Tensor-core pieces of the batched dot products: D(16x8, fp32) += A(16x16) * B(16x8) on 16-bit
+// inputs with only rows 0..7 of A in use (the other half of the fragment is zero): A = eight
+// weight rows x 16 columns, B = 16 columns x eight tokens, D = eight rows x eight tokens.
+// Products of 16-bit floats are exact in fp32 and the sums are fp32.
+template <typename T>
+struct Mma8;
+template <>
+struct Mma8<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+  }
+};
+template <>
+struct Mma8<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+  }
+};
+template <>
+struct Mma8<float> {  // fp32 weights never take this path
+  static __device__ __forceinline__ void run(float (&)[4], uint32_t, uint32_t, uint32_t, uint32_t) {}
+};
+// Two 8x8 matrices of 16-bit values from shared memory: lanes 0-7 give the row addresses of the
+// first, lanes 8-15 of the second (16 bytes per row); lane l receives elements
+// [l / 4][2 * (l % 4) .. + 1] of each.
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r0), "=r"(r1)
+               : "r"(addr));
 }
 
 // Copy the B activation vectors into shared memory (all threads of the CTA).

@@ -42,14 +42,15 @@ def test_single_rank_exchange_matches_the_plain_stack_and_the_oracle(H, I, L, B,
     torch.cuda.synchronize()
     # fp32 sums in a different order; 16-bit storage rounds them differently now and then and a
     # gate value next to the threshold may then flip in a later layer
-    tight = 1e-5 if dt == torch.float32 else 2e-2
+    # (bf16 keeps 8 bits: over three layers a few flipped gates move the result by a few percent)
+    tight = {torch.float32: 1e-5, torch.float16: 2e-2, torch.bfloat16: 5e-2}[dt]
     assert O.rel_l2(to_np(fused.resid), to_np(plain.resid)) <= tight
     assert O.rel_l2(to_np(fused.x), to_np(plain.x)) <= tight
     bf16 = lambda a: torch.from_numpy(np.asarray(a, np.float32)).to(torch.bfloat16).float().numpy()
     rnd = {torch.float16: np.float16, torch.float32: None, torch.bfloat16: bf16}[dt]
     xe, re_, _ = O.mlp_stack(to_np(x0), [(to_np(l.wg), to_np(l.wu), to_np(l.wdt).T) for l in layers],
                              [l.threshold for l in layers], round_to=rnd)
-    tol = 1e-3 if dt == torch.float32 else 2e-2
+    tol = {torch.float32: 1e-3, torch.float16: 2e-2, torch.bfloat16: 5e-2}[dt]
     assert O.rel_l2(to_np(fused.resid), re_) <= tol
     assert O.rel_l2(to_np(fused.x), xe) <= tol
     fused.close()

@@ -40,7 +40,7 @@ def main():
             xe, re_, _ = O.mlp_stack(to_np(x0), [(to_np(l.wg), to_np(l.wu), to_np(l.wdt).T)
                                                  for l in full], [l.threshold for l in full],
                                      round_to=rnd)
-            tol = 1e-3 if dt == torch.float32 else 2e-2
+            tol = {torch.float32: 1e-3, torch.float16: 2e-2, torch.bfloat16: 5e-2}[dt]
             e_r, e_x = O.rel_l2(to_np(stack.resid), re_), O.rel_l2(to_np(stack.x), xe)
             print(f"H {H} I {I} L {L} B {B} {dt}: resid {e_r:.2e} x {e_x:.2e} status {status} "
                   f"identical {same}", flush=True)
