@@ -88,17 +88,20 @@ struct MegaArgs {
 };
 
 // Exchange buffer of one rank (see MegaArgs::xchg).  Header: one arrival counter per SOURCE rank
-// (a source's CTAs arrive once per layer, after their stores into this buffer), the counters'
-// common value at the start of the current launch, and the running number of layers (its low
-// bit selects the slot set, so consecutive layers alternate sets across launches too).
-// Then slots[2][kMaxRanks][kMegaMaxB * H] fp32: slots[s][p] = rank p's partial sums.
+// (a source's CTAs bump it once per layer after their stores into this buffer — a hint that
+// the data is probably there, not a guarantee), the counters' common value at the start of the
+// current launch, and the running number of layers (its low bit selects the slot set, so
+// consecutive layers alternate sets across launches too; plus one it is the tag of the layer's
+// data).  Then slots[2][kMaxRanks][kMegaMaxB * H] of 8-byte (value, tag) pairs: slots[s][p] =
+// rank p's partial sums.  A pair is written with one store, so a reader that finds the tag it
+// expects has the value that belongs to it: no fence orders data against flags, on either side.
 enum { XCH_ARRIVED = 0 /* [kMaxRanks] */, XCH_BASE = 16, XCH_LAYERS = 17, XCH_HDR_BYTES = 256 };
 constexpr int kMegaMaxB = 4;
 __host__ __device__ inline size_t xchg_bytes(int H) {
-  return XCH_HDR_BYTES + sizeof(float) * 2 * (size_t)kMaxRanks * kMegaMaxB * H;
+  return XCH_HDR_BYTES + sizeof(uint2) * 2 * (size_t)kMaxRanks * kMegaMaxB * H;
 }
-__host__ __device__ inline float* xchg_slot(unsigned char* base, int set, int src, int H) {
-  return reinterpret_cast<float*>(base + XCH_HDR_BYTES) +
+__host__ __device__ inline uint2* xchg_slot(unsigned char* base, int set, int src, int H) {
+  return reinterpret_cast<uint2*>(base + XCH_HDR_BYTES) +
          ((size_t)set * kMaxRanks + src) * kMegaMaxB * H;
 }
 
@@ -143,8 +146,16 @@ __device__ __forceinline__ bool grid_wait(const unsigned* ctr, unsigned target,
 // The same pair at system scope, for counters that other GPUs add to over NVLink (the counter
 // polled is always in this GPU's own memory).  Other ranks' kernels are launched by other
 // processes, so the bound is several times the local one.
-__device__ __forceinline__ void peer_arrive(unsigned* ctr) {
-  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+__device__ __forceinline__ void peer_arrive(unsigned* ctr) {  // a hint: see the exchange buffer
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
 }
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   unsigned v;
@@ -460,13 +471,20 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (ok) {
           float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
           const int set = (int)((xl0 + (unsigned)l) & 1u);
+          const unsigned tag = xl0 + (unsigned)l + 1u;
           for (int b = 0; b < B; ++b) {
             for (int g = own_lo + lane; g < own_hi; g += 32) {
               float4* src = reinterpret_cast<float4*>(accp + (size_t)b * H) + g;
               const float4 v = __ldcg(src);
               *src = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int p = 0; p < K; ++p)
-                reinterpret_cast<float4*>(xchg_slot(A.xchg[p], set, A.rank, H) + (size_t)b * H)[g] = v;
+              const uint4 lo4 = make_uint4(__float_as_uint(v.x), tag, __float_as_uint(v.y), tag);
+              const uint4 hi4 = make_uint4(__float_as_uint(v.z), tag, __float_as_uint(v.w), tag);
+              for (int p = 0; p < K; ++p) {
+                uint4* dst = reinterpret_cast<uint4*>(xchg_slot(A.xchg[p], set, A.rank, H) +
+                                                      (size_t)b * H + 4 * (size_t)g);
+                dst[0] = lo4;
+                dst[1] = hi4;
+              }
             }
           }
           __syncwarp();
@@ -509,9 +527,10 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       consumer_bar_sync();
       CATS_STAMP(0, 4, (l + 1 == L / 2) && tid == 0);
       ok = !s_abort;
-      const float* accp = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H)
-                            : ws.acc32 + (size_t)(l & 1) * kMaxB * H;
-      const size_t src_stride = (size_t)kMegaMaxB * H;  // between source ranks' slots
+      const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
+      const uint2* slots = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H) : nullptr;
+      const unsigned tag = xl0 + (unsigned)l + 1u;
+      const size_t src_stride = (size_t)kMegaMaxB * H;  // pairs between source ranks' slots
       const int ngrp = ngrp_all;
       const T* nw = reinterpret_cast<const T*>(P.nw[l]);
       constexpr int KV = 4;
@@ -519,33 +538,58 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         float ss = 0.f;
         for (int g0 = 0; g0 < ngrp && ok; g0 += KV * kConsumerThreads) {
           float4 a[KV];
+          if (!K) {
 #pragma unroll
-          for (int q = 0; q < KV; ++q) {
-            const int g = g0 + q * kConsumerThreads + tid;
-            a[q] = (g < ngrp) ? __ldcg(reinterpret_cast<const float4*>(accp + (size_t)b * H) + g)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-          // the other ranks' partial sums, in rank order on every GPU (identical x everywhere);
-          // four sources' loads in flight at a time
-          for (int p0 = 1; p0 < K; p0 += 4) {
-            float4 t[4][KV];
+            for (int q = 0; q < KV; ++q) {
+              const int g = g0 + q * kConsumerThreads + tid;
+              a[q] = (g < ngrp) ? __ldcg(reinterpret_cast<const float4*>(accp + (size_t)b * H) + g)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          } else {
+            // The ranks' partial sums, added in rank order on every GPU (identical x everywhere),
+            // two sources' loads in flight at a time.  Every pair carries the layer's tag: a
+            // pair that has not arrived yet (the counters are only a hint) is simply read again.
 #pragma unroll
-            for (int pp = 0; pp < 4; ++pp)
+            for (int q = 0; q < KV; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p0 = 0; p0 < K && ok; p0 += 2) {
+              uint4 u[2][KV][2];
+              const long long t0 = clock64();
+              for (;;) {
+                bool good = true;
 #pragma unroll
-              for (int q = 0; q < KV; ++q) {
-                const int g = g0 + q * kConsumerThreads + tid;
-                t[pp][q] = (p0 + pp < K && g < ngrp)
-                               ? __ldcg(reinterpret_cast<const float4*>(
-                                            accp + (size_t)(p0 + pp) * src_stride + (size_t)b * H) + g)
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int pp = 0; pp < 2; ++pp)
+#pragma unroll
+                  for (int q = 0; q < KV; ++q) {
+                    const int g = g0 + q * kConsumerThreads + tid;
+                    if (p0 + pp < K && g < ngrp) {
+                      const uint2* src = slots + (size_t)(p0 + pp) * src_stride + (size_t)b * H + 4 * (size_t)g;
+                      u[pp][q][0] = ld_volatile_v4(src);
+                      u[pp][q][1] = ld_volatile_v4(src + 2);
+                    } else {
+                      u[pp][q][0] = u[pp][q][1] = make_uint4(0u, tag, 0u, tag);
+                    }
+                  }
+#pragma unroll
+                for (int pp = 0; pp < 2; ++pp)
+#pragma unroll
+                  for (int q = 0; q < KV; ++q)
+                    good = good && u[pp][q][0].y == tag && u[pp][q][0].w == tag &&
+                           u[pp][q][1].y == tag && u[pp][q][1].w == tag;
+                if (good) break;
+                if (s_abort || clock64() - t0 > 4 * kWaitCycles) {
+                  s_abort = 1;
+                  ok = false;
+                  break;
+                }
               }
 #pragma unroll
-            for (int pp = 0; pp < 4; ++pp)
+              for (int pp = 0; pp < 2; ++pp)
 #pragma unroll
-              for (int q = 0; q < KV; ++q) {
-                a[q].x += t[pp][q].x; a[q].y += t[pp][q].y;
-                a[q].z += t[pp][q].z; a[q].w += t[pp][q].w;
-              }
+                for (int q = 0; q < KV; ++q) {
+                  a[q].x += __uint_as_float(u[pp][q][0].x); a[q].y += __uint_as_float(u[pp][q][0].z);
+                  a[q].z += __uint_as_float(u[pp][q][1].x); a[q].w += __uint_as_float(u[pp][q][1].z);
+                }
+            }
           }
 #pragma unroll
           for (int q = 0; q < KV; ++q) {
