@@ -286,6 +286,9 @@ def run_gpu_arm(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
+        # NCCL prints its version line to stdout at this debug level; stdout carries the JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     H, I, dtype, L, s = workload_config(args)
     B = args.batch

@@ -378,6 +378,26 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
       p.S = cand;
     }
   }
+  if (p.mma_dot) {
+    // the tensor-core path has no dot-owner warps: take the deepest ring that three or four
+    // producer threads divide (an extra stage is worth about as much as the fourth producer)
+    int best = 0, best_score = -1;
+    for (int cand = smax; cand >= 8 && cand >= smax - 7; --cand) {
+      const int np = cand % 4 == 0 ? 4 : cand % 3 == 0 ? 3 : 0;
+      if (!np) continue;
+      const int score = 2 * cand + (np == 4 ? 3 : 0);
+      if (score > best_score) {
+        best_score = score;
+        best = cand;
+      }
+    }
+    if (best) {
+      p.S = best;
+      p.cw = 1;
+      for (int d = 1; d <= kConsumerWarps; ++d)
+        if (best % d == 0) p.cw = d;
+    }
+  }
 #ifdef CATS_PHASE_TIMING
   if (const char* e = getenv("CATS_DEV_S")) {  // development: force the stage count
     p.S = atoi(e);
@@ -452,7 +472,7 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
                     cudaStream_t st) {
   A.S = p.S;
   A.cw = p.cw;
-  A.npw = (p.S % kMegaProducers == 0) ? kMegaProducers : 2;
+  A.npw = (p.S % kMegaProducers == 0) ? kMegaProducers : (p.S % 3 == 0) ? 3 : 2;
   A.bulk_flush = p.bulk_flush;
   A.mma_dot = p.mma_dot;
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;

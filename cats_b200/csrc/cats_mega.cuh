@@ -36,6 +36,10 @@
 
 #include <type_traits>
 
+#ifndef CATS_ONE_FMA_B1
+#define CATS_ONE_FMA_B1 0
+#endif
+
 #include "cats_tma.cuh"
 
 namespace cats {
@@ -822,7 +826,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           // all loads of a column group first (kDG independent 16-byte loads in flight per
           // thread), then the FMAs: with two warps per scheduler nothing else hides the latency
           // batches: the scalar rounded to the storage type, one FMA per weight (prep1 / axpy1)
-          constexpr bool kOneFma = BT >= 2 && sizeof(T) == 2;
+          constexpr bool kOneFma = (BT >= 2 || CATS_ONE_FMA_B1) && sizeof(T) == 2;
           typedef typename std::conditional<kOneFma, uint32_t, typename V::Scalar>::type HScalar;
           HScalar hb[kDG][BT];
           const uint4* rowp[kDG];
