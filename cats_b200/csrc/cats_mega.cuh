@@ -467,9 +467,10 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       }
       if (K) {
         // Tensor parallel: once every CTA of this GPU has added its share of layer l, send this
-        // CTA's slice of the sums to every rank's slot for this rank (plain stores into peer
-        // memory; the release at system scope by the arriving lanes publishes them), and clear
-        // the slice for layer l+2 (nobody else reads the accumulators in this mode).
+        // CTA's slice of the sums to every rank's slot for this rank (plain stores of
+        // (value, tag) pairs into peer memory, then a relaxed bump of the hint counters), and
+        // clear the slice for layer l+2 (nobody else reads the accumulators in this mode; the
+        // clearing reaches the other CTAs through the list and layer barriers of layer l+1).
         if (ok) ok = grid_wait(obar, otarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
@@ -521,8 +522,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // computes the whole vector for itself; global outputs are written in disjoint slices.
     auto next_x = [&](int l, bool last) {
       // single GPU: all CTAs' sums are in the accumulators once the layer barrier completes;
-      // tensor parallel: every rank's partial sums are in this GPU's slots once every source
-      // rank's G CTAs have arrived (thread p polls source p's counter)
+      // tensor parallel: every rank's partial sums are (most probably) in this GPU's slots once
+      // every source rank's G CTAs have bumped their counter (thread p polls source p's); the
+      // tags of the pairs decide
       if (K) {
         if (tid < K && ok) peer_wait(xflag + XCH_ARRIVED + tid, xbase + (unsigned)(l + 1) * G, &s_abort);
       } else {

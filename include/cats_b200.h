@@ -207,9 +207,9 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
  * the unsharded ones) and runs cats_tp_mlp_stack at the same time as its peers: the persistent
  * kernel of cats_mlp_stack, whose CTAs, at the end of every layer, store their slice of this
  * rank's partial sums straight into every peer's exchange buffer over NVLink (plain peer stores
- * published by a release at system scope; no TMA involved), wait until every rank's partials
- * have arrived in their own buffer, and add them in rank order, so that every rank computes
- * bit-identical residuals and inputs for the next layer.  x_io / resid [B, H] as for
+ * of 8-byte value + layer-tag pairs, so no fence is needed on either side; no TMA involved),
+ * wait until every rank's partials have arrived in their own buffer, and add them in rank
+ * order, so that every rank computes bit-identical residuals and inputs for the next layer.  x_io / resid [B, H] as for
  * cats_mlp_stack, replicated on every rank.  B <= 4.
  *
  * exchange[p] (host array of nranks device pointers) is rank p's exchange buffer as mapped into
