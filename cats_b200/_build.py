@@ -57,21 +57,35 @@ def is_current() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if the sources changed; returns the path of the shared object."""
+    """Compile the library if the sources changed; returns the path of the shared object.
+
+    Safe to call from several processes at once (the ranks of a multi-GPU job import the package
+    at the same time): a file lock serialises them, the loser of the race finds the library
+    current, and the shared object is moved into place in one step."""
+    import fcntl
+
     if not force and is_current():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-o", LIB_PATH]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    log = proc.stdout + proc.stderr
-    with open(os.path.join(HERE, "libcats_b200.buildlog"), "w") as f:
-        f.write(" ".join(cmd) + "\n" + log)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + log[-4000:])
-    if verbose:
-        print(log)
-    with open(STAMP_PATH, "w") as f:
-        f.write(source_digest())
+    with open(os.path.join(HERE, "libcats_b200.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current():
+            return LIB_PATH
+        tmp = LIB_PATH + f".tmp{os.getpid()}"
+        cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-o", tmp]
+        cmd += [os.path.join(CSRC, s) for s in SOURCES]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        log = proc.stdout + proc.stderr
+        with open(os.path.join(HERE, "libcats_b200.buildlog"), "w") as f:
+            f.write(" ".join(cmd) + "\n" + log)
+        if proc.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+            raise RuntimeError("nvcc failed:\n" + log[-4000:])
+        if verbose:
+            print(log)
+        os.replace(tmp, LIB_PATH)
+        with open(STAMP_PATH, "w") as f:
+            f.write(source_digest())
     return LIB_PATH
 
 
