@@ -47,7 +47,7 @@ WORKLOADS = {
 # dram__bytes_read + dram__bytes_write per layer of k_cats_mega for the default workload, from the
 # ncu capture summarised in profiles/k_cats_mega_mistral7b_fp16_s50_ncu_full.md (2 layers captured;
 # traffic is proportional to the number of layers)
-NCU_TRAFFIC_PER_LAYER = {("mistral7b", 0.5, 1): 236.5e6}
+NCU_TRAFFIC_PER_LAYER = {("mistral7b", 0.5, 1): 236.7e6}
 METRIC = "cats_mlp_stack_decode_tokens_per_s"
 UNIT = "tokens/s"
 
