@@ -1,9 +1,9 @@
 """Generate tests/golden/*.npz by running the REFERENCE's own module on small seeded inputs.
 
-Run it where the reference checkout is available (path in $CATS_REFERENCE, default
-/root/reference):
+Run it where a checkout of the reference (ScalingIntelligence/CATS) is available, with its path
+in $CATS_REFERENCE:
 
-    python tests/golden/make_golden.py
+    CATS_REFERENCE=<path to the CATS checkout> python tests/golden/make_golden.py
 
 The reference module (experiments/models/sparse_silu/ugly_utils.py) imports plotting, training
 and kernel packages that the decode path never touches (matplotlib, seaborn, peft, trl and the
@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("CATS_REFERENCE", "/root/reference")
+REF = os.environ.get("CATS_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "..", "reference"))
 
 
 def import_reference():
