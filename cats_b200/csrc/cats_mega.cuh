@@ -50,7 +50,7 @@ constexpr int kMaxRanks = 8;                   // GPUs of one tensor-parallel gr
 constexpr int kMegaProducers = 4;  // issuing threads (one per warp); the host uses 2 when 4 does not divide S
 constexpr int kMegaWarps = kConsumerWarps + kMegaProducers + 2;  // + publisher + lister
 constexpr int kMegaThreads = kMegaWarps * 32;
-constexpr int kParts = 3;                      // a layer's neurons are processed in this many parts
+constexpr int kParts = 3;                      // a layer's neurons are processed in up to this many parts
 constexpr int kSegHalfStride = kMaxSeg / 4;   // seg_count slots of part p start at p * this
 
 enum { STATUS_WAIT_TIMEOUT_MEGA = 3 };
@@ -78,6 +78,8 @@ struct MegaArgs {
   int npw;               // producer threads in use (divides S)
   int bulk_flush;        // 1: accumulators leave through shared memory and TMA bulk reduces
   int mma_dot;           // 1: gate / up dot products of eight rows at a time on the tensor cores
+  int parts;             // parts per layer (1..kParts): more parts hide the list latency behind
+                         // other parts' rows, fewer parts mean fewer grid barriers per layer
   unsigned s_magic;      // floor(2^32 / S) + 1: item -> (ring cycle, slot) without a division
   float eps;
   const void* x_in;  // [B,H] input of layer 0
@@ -110,8 +112,8 @@ __host__ __device__ inline uint2* xchg_slot(unsigned char* base, int set, int sr
 }
 
 // Rows [lo, hi) of half h out of I.
-__host__ __device__ inline int half_row0(int h, int I) {
-  return (int)(((long long)I * h) / kParts);
+__host__ __device__ inline int half_row0(int h, int I, int parts) {
+  return (int)(((long long)I * h) / parts);
 }
 
 // ---- grid barrier on a monotonic counter ------------------------------------------------------
@@ -195,7 +197,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   __shared__ int s_cnt[kParts];
   __shared__ int s_pref[kMegaMaxGrid];
 
-  const int L = A.L, B = A.B, H = A.H, I = A.I, S = A.S, cw = A.cw;
+  const int L = A.L, B = A.B, H = A.H, I = A.I, S = A.S, cw = A.cw, NP = A.parts;
   const uint32_t row_bytes = (uint32_t)H * sizeof(T);
   const int nvec = H / N;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -278,11 +280,11 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
 
   // this CTA's gate segment of half h
   auto seg_lo = [&](int h) {
-    const int lo = half_row0(h, I), hi = half_row0(h + 1, I);
+    const int lo = half_row0(h, I, NP), hi = half_row0(h + 1, I, NP);
     return lo + seg_row0(c, G, hi - lo);
   };
   auto seg_hi = [&](int h) {
-    const int lo = half_row0(h, I), hi = half_row0(h + 1, I);
+    const int lo = half_row0(h, I, NP), hi = half_row0(h + 1, I, NP);
     return lo + seg_row0(c + 1, G, hi - lo);
   };
 
@@ -308,7 +310,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         const T* Wg = reinterpret_cast<const T*>(P.wg[l]);
         const T* Wu = reinterpret_cast<const T*>(P.wu[l]);
         const T* Wd = reinterpret_cast<const T*>(P.wdt[l]);
-        for (int h = 0; h < kParts && ok; ++h) {
+        for (int h = 0; h < NP && ok; ++h) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
           // own items only: j == (p - k) mod npw, stepping by npw (no division per row)
           for (int j = ((p - k) % npw + npw) % npw; j < R && ok; j += npw) {
@@ -323,7 +325,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           k += R;
           CATS_STAMP(1, 1 + h, tl && h < 2);
         }
-        for (int h = 0; h < kParts && ok; ++h) {
+        for (int h = 0; h < NP && ok; ++h) {
           if (!mbar_wait(lready_u + 8u * h, l & 1, &s_abort)) {
             ok = false;
             break;
@@ -355,7 +357,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     bool ok = true;
     for (int l = 0; l < L; ++l) {
       const float thr = P.thr[l];
-      for (int h = 0; h < kParts; ++h) {
+      for (int h = 0; h < NP; ++h) {
         const bool tl = (l == L / 2) && lane == 0;
         // this CTA's gate values of part h are in: ballot / popc compaction, publish, arrive
         if (ok) ok = mbar_wait(gdone_u + 8u * h, l & 1, &s_abort);
@@ -406,7 +408,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // =========================================================================== lister
     bool ok = true;
     for (int l = 0; l < L; ++l) {
-      for (int h = 0; h < kParts; ++h) {
+      for (int h = 0; h < NP; ++h) {
         const bool tl = (l == L / 2) && lane == 0;
         // all CTAs have published part h: scan the counts, take this CTA's balanced share
         if (ok) ok = grid_wait(gbar + h, gtarget(l), &s_abort);
@@ -439,7 +441,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         const int n = run;
         const int p0 = (int)(((long long)c * n) / G), p1 = (int)(((long long)(c + 1) * n) / G);
         const int cnt = ok ? p1 - p0 : 0;
-        const int hlo = half_row0(h, I), hrows = half_row0(h + 1, I) - hlo;
+        const int hlo = half_row0(h, I, NP), hrows = half_row0(h + 1, I, NP) - hlo;
         for (int j = lane; j < cnt; j += 32) {
           const int pos = p0 + j;
           int lo = 0, hi = G - 1;  // smallest segment with s_pref > pos
@@ -715,7 +717,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           for (int i = 0; i < N; ++i) acc[g][t][i] = 0.f;
 
       // ---- gate rows of the two halves ---------------------------------------------------------
-      for (int h = 0; h < kParts; ++h) {
+      for (int h = 0; h < NP; ++h) {
         const int r0 = seg_lo(h), R = seg_hi(h) - r0;
         float* sv = s_val + (size_t)h * A.rmax * BT;
         if (mma_dot) {
@@ -760,7 +762,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       }
 
       // ---- up and down rows of the two halves ----------------------------------------------------
-      for (int h = 0; h < kParts; ++h) {
+      for (int h = 0; h < NP; ++h) {
         CATS_STAMP(0, 6 + 4 * h, tl && tid == 0 && h < 2);
         if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
         CATS_STAMP(0, 7 + 4 * h, tl && tid == 0 && h < 2);

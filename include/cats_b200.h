@@ -69,10 +69,12 @@ int cats_sm_count(void);
  * (default 1; 0 forces the direct-load kernels).  "ring_kb": shared-memory ring per TMA kernel in
  * KiB (default 200).  "pdl" (0/1): launch with programmatic dependent launch (default 1).
  * "mega" (0/1): run cats_mlp / cats_mlp_stack as one persistent cooperative kernel where the
- * shape allows (default 1; 0 = one stage-1 and one stage-2/3 launch per layer).  The same values
- * are read once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL
- * and CATS_B200_MEGA.  No reference
- * counterpart.
+ * shape allows (default 1; 0 = one stage-1 and one stage-2/3 launch per layer).  Inside the
+ * persistent kernel: "bulk_flush" (0/1, default 1: accumulators leave through TMA bulk reduces),
+ * "mma_dot" (0/1, default 1: tensor-core dot products for batches of 2-4 with 16-bit weights),
+ * "parts" (0 = automatic, or 1..3 parts per layer).  The same values are read once from the
+ * environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL, CATS_B200_MEGA,
+ * CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT and CATS_B200_PARTS.  No reference counterpart.
  */
 int cats_set_option(const char* name, int value);
 
