@@ -286,9 +286,9 @@ def run_gpu_arm(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        # NCCL prints its version line to stdout at this debug level; stdout carries the JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # NCCL prints its version line (debug level VERSION and above) to stdout unless it is
+        # given a file: stdout carries the one JSON line, so send NCCL's output to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     H, I, dtype, L, s = workload_config(args)
     B = args.batch
