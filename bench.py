@@ -227,7 +227,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def config_block(args, H, I, dtype, L, s, world):
@@ -286,9 +286,6 @@ def run_gpu_arm(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        # NCCL prints its version line (debug level VERSION and above) to stdout unless it is
-        # given a file: stdout carries the one JSON line, so send NCCL's output to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     H, I, dtype, L, s = workload_config(args)
     B = args.batch
@@ -549,12 +546,35 @@ def run_gpu_arm(args):
         line["roofline"]["stats_kernels"] = stats
     if world > 1:
         line["tp"] = {"mode": tp_mode, "nccl_allreduce_variant": nccl_variant}
-    print(json.dumps(line), flush=True)
+    emit(line)
     leave()
+
+
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keep stdout for the one JSON line: whatever libraries print on file descriptor 1 from now
+    on (NCCL writes its version line there) goes to stderr instead."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, data)
 
 
 def main():
     args = parse_args()
+    claim_stdout()
     if args.impl == "reference":
         run_reference_arm(args)
     else:
