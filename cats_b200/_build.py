@@ -17,18 +17,20 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libcats_b200.so")
 STAMP_PATH = os.path.join(HERE, "libcats_b200.stamp")
-SOURCES = ["cats_abi.cu"]
-HEADERS = [
-    os.path.join(CSRC, "cats_common.cuh"),
-    os.path.join(CSRC, "cats_kernels.cuh"),
-    os.path.join(CSRC, "cats_tma.cuh"),
-    os.path.join(CSRC, "cats_mega.cuh"),
-    os.path.join(ROOT, "include", "cats_b200.h"),
-]
+OBJ_DIR = os.path.join(HERE, "_obj")
+# translation units: (source, extra defines, object name).  The kernels are instantiated once per
+# element type in units of their own so that the library compiles in parallel.
+UNITS = [("cats_abi.cu", [], "cats_abi.o")]
+for _id, _name in ((0, "f32"), (1, "f16"), (2, "bf16")):
+    UNITS.append(("cats_inst_stage.cu", [f"-DCATS_ELEM_ID={_id}"], f"cats_inst_stage_{_name}.o"))
+    UNITS.append(("cats_inst_mega.cu", [f"-DCATS_ELEM_ID={_id}"], f"cats_inst_mega_{_name}.o"))
+SOURCES = sorted({u[0] for u in UNITS})
+HEADERS = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
+    os.path.join(ROOT, "include", "cats_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "--shared", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC",
     "-Xptxas", "-v",
 ]
 
@@ -70,17 +72,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
         fcntl.flock(lock, fcntl.LOCK_EX)
         if not force and is_current():
             return LIB_PATH
+        from concurrent.futures import ThreadPoolExecutor
+
+        os.makedirs(OBJ_DIR, exist_ok=True)
         tmp = LIB_PATH + f".tmp{os.getpid()}"
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-o", tmp]
-        cmd += [os.path.join(CSRC, s) for s in SOURCES]
-        proc = subprocess.run(cmd, capture_output=True, text=True)
-        log = proc.stdout + proc.stderr
+        nvcc = _nvcc()
+
+        def compile_unit(unit):
+            src, defines, obj = unit
+            cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", os.path.join(ROOT, "include"), "-c",
+                   os.path.join(CSRC, src), "-o", os.path.join(OBJ_DIR, obj)]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            return proc.returncode, " ".join(cmd) + "\n" + proc.stdout + proc.stderr
+
+        with ThreadPoolExecutor(max_workers=min(len(UNITS), os.cpu_count() or 1)) as pool:
+            results = list(pool.map(compile_unit, UNITS))
+        log = "\n".join(r[1] for r in results)
+        rc = max(r[0] for r in results)
+        if rc == 0:
+            cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "--shared", "-o", tmp]
+            cmd += [os.path.join(OBJ_DIR, u[2]) for u in UNITS]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            rc = proc.returncode
+            log += "\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr
         with open(os.path.join(HERE, "libcats_b200.buildlog"), "w") as f:
-            f.write(" ".join(cmd) + "\n" + log)
-        if proc.returncode != 0:
+            f.write(log)
+        if rc != 0:
             if os.path.exists(tmp):
                 os.remove(tmp)
-            raise RuntimeError("nvcc failed:\n" + log[-4000:])
+            raise RuntimeError("nvcc failed:\n" + log[-6000:])
         if verbose:
             print(log)
         os.replace(tmp, LIB_PATH)

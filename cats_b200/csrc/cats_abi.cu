@@ -8,19 +8,12 @@
 
 #include <mutex>
 
-#include "cats_mega.cuh"
+#include "cats_run.cuh"
 #include "cats_stats.cuh"
 
-namespace {
+namespace cats {
 
-using namespace cats;
-
-thread_local cudaError_t g_last_cuda = cudaSuccess;
-
-struct DevInfo {
-  int sms = 0;
-  int max_smem_optin = 0;
-};
+int g_use_pdl = 1;
 
 // Per-device properties, queried once per device (no allocation involved).
 const DevInfo& dev_info() {
@@ -37,6 +30,36 @@ const DevInfo& dev_info() {
   }
   return info[dev];
 }
+
+// the per-type launchers are instantiated in cats_inst_stage.cu / cats_inst_mega.cu
+#define CATS_EXTERN_INST(T)                                                                         \
+  extern template cudaError_t inst_gate<T>(const void*, const void*, WsPtrs, int, int, int, float,  \
+                                           void*, uint8_t*, cudaStream_t);                          \
+  extern template cudaError_t inst_updown<T>(int, const void*, const void*, const void*, WsPtrs,    \
+                                             int, int, int, void*, int, void*, void*, const void*,  \
+                                             float, void*, cudaStream_t);                           \
+  extern template cudaError_t inst_rows_gemv<T>(const void*, const void*, int, int, int, void*,     \
+                                                cudaStream_t);                                      \
+  extern template cudaError_t inst_gate_tma<T>(const TmaPlan&, const void*, const void*, WsPtrs,    \
+                                               int, int, int, float, void*, uint8_t*,               \
+                                               cudaStream_t);                                       \
+  extern template cudaError_t inst_updown_tma<T>(const TmaPlan&, const void*, const void*,          \
+                                                 const void*, WsPtrs, int, int, int, void*, int,    \
+                                                 void*, void*, const void*, float, cudaStream_t);   \
+  extern template cudaError_t inst_mega<T>(const MegaPlan&, const MegaParams&, const MegaArgs&,     \
+                                           WsPtrs, cudaStream_t);
+CATS_EXTERN_INST(float)
+CATS_EXTERN_INST(__half)
+CATS_EXTERN_INST(__nv_bfloat16)
+#undef CATS_EXTERN_INST
+
+}  // namespace cats
+
+namespace {
+
+using namespace cats;
+
+thread_local cudaError_t g_last_cuda = cudaSuccess;
 
 int esize(int dtype) { return dtype == CATS_F32 ? 4 : 2; }
 int vecn(int dtype) { return dtype == CATS_F32 ? 4 : 8; }
@@ -62,116 +85,13 @@ int cuda_status(cudaError_t e) {
   return CATS_ERR_CUDA;
 }
 
-int g_use_pdl = 1;  // cats_set_option("pdl", 0) launches without programmatic dependencies
-
-// Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while
-// its predecessor drains; every kernel here calls griddepcontrol.wait before touching data.
-template <typename... KArgs, typename... Args>
-cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                   cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = g_use_pdl ? 1 : 0;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
-  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
-int batch_tile(int B) { return B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : B <= 8 ? 8 : 16; }
-
-// Call F<T, BT>::run(args...) for the runtime (dtype, B).
-#define CATS_DISPATCH_BT(T, BT_, FN, ...)         \
-  switch (BT_) {                                  \
-    case 1: return FN<T, 1>(__VA_ARGS__);         \
-    case 2: return FN<T, 2>(__VA_ARGS__);         \
-    case 4: return FN<T, 4>(__VA_ARGS__);         \
-    case 8: return FN<T, 8>(__VA_ARGS__);         \
-    default: return FN<T, 16>(__VA_ARGS__);       \
-  }
-#ifdef CATS_DEV_HALF_ONLY
-#define CATS_DISPATCH(dtype, BT_, FN, ...) \
-  do { if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__); return FN<__half, 2>(__VA_ARGS__); } while (0)
-#else
-#define CATS_DISPATCH(dtype, BT_, FN, ...)                                     \
-  do {                                                                         \
-    if ((dtype) == CATS_F32) { CATS_DISPATCH_BT(float, BT_, FN, __VA_ARGS__) } \
-    if ((dtype) == CATS_F16) { CATS_DISPATCH_BT(__half, BT_, FN, __VA_ARGS__) } \
-    CATS_DISPATCH_BT(__nv_bfloat16, BT_, FN, __VA_ARGS__)                      \
+// FN<T>(args...) for the runtime dtype
+#define CATS_DISPATCH(dtype, FN, ...)                                  \
+  do {                                                                 \
+    if ((dtype) == CATS_F32) return FN<float>(__VA_ARGS__);            \
+    if ((dtype) == CATS_F16) return FN<__half>(__VA_ARGS__);           \
+    return FN<__nv_bfloat16>(__VA_ARGS__);                             \
   } while (0)
-#endif
-
-// ---- grid sizing --------------------------------------------------------------------------
-int gate_segments(int I) {
-  int g = dev_info().sms * 2;
-  if (g > kMaxSeg) g = kMaxSeg;
-  const int by_rows = (I + 15) / 16;  // at least ~16 rows (two per warp) per CTA
-  if (g > by_rows) g = by_rows;
-  return g < 1 ? 1 : g;
-}
-
-int updown_ctas(int I) {
-  int g = dev_info().sms * 2;
-  const int by_rows = (I + 7) / 8;
-  if (g > by_rows) g = by_rows;
-  return g < 1 ? 1 : g;
-}
-
-template <typename T, int BT>
-cudaError_t run_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, float thr,
-                     void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
-  const int nseg = gate_segments(I);
-  const int rmax = (I + nseg - 1) / nseg;
-  const size_t smem = sizeof(float) * (size_t)rmax * BT;
-  return launch(k_gate<T, BT>, dim3(nseg), dim3(kThreads), smem, st, (const T*)x, (const T*)Wg,
-                ws, B, H, I, thr, (T*)gate_dense, flag_dense);
-}
-
-template <typename T, int BT, int MODE>
-cudaError_t run_updown_mode(const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
-                            int H, int I, void* out, int out_mode, void* resid, void* x_next,
-                            const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
-  const int G = updown_ctas(I);
-  const int cap = (I + G - 1) / G;
-  const size_t smem = (size_t)(cap + kRU) * (sizeof(int) + sizeof(float) * BT);
-  return launch(k_updown<T, BT, MODE>, dim3(G), dim3(kThreads), smem, st, (const T*)x,
-                (const T*)Wu, (const T*)WdT, ws, B, H, I, cap, (T*)out, out_mode, (T*)resid,
-                (T*)x_next, (const T*)norm_w, eps, (T*)inter_dense);
-}
-
-template <typename T, int BT>
-cudaError_t run_updown(int mode, const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
-                       int H, int I, void* out, int out_mode, void* resid, void* x_next,
-                       const void* norm_w, float eps, void* inter_dense, cudaStream_t st) {
-  if (mode == 1)
-    return run_updown_mode<T, BT, 1>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
-                                     eps, inter_dense, st);
-  if (mode == 2)
-    return run_updown_mode<T, BT, 2>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
-                                     eps, inter_dense, st);
-  return run_updown_mode<T, BT, 3>(x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w,
-                                   eps, inter_dense, st);
-}
-
-template <typename T, int BT>
-cudaError_t run_rows_gemv(const void* xs, const void* W, int B, int K, int R, void* out,
-                          cudaStream_t st) {
-  int g = dev_info().sms * 4;
-  const int need = (R + kWarps * 2 - 1) / (kWarps * 2);
-  if (g > need) g = need;
-  return launch(k_rows_gemv<T, BT>, dim3(g), dim3(kThreads), 0, st, (const T*)xs, (const T*)W, B,
-                K, R, (T*)out);
-}
 
 // ---- tuning knobs (cats_set_option) ------------------------------------------------------------
 struct Options {
@@ -196,12 +116,6 @@ Options& options() {
   }();
   return o;
 }
-
-struct TmaPlan {
-  bool ok = false, xs = false;
-  int S = 0, grid = 0, sr = 1, nvt = 1, cap = 0, rmax = 0, cw = 1, pw = 1;
-  size_t smem = 0;
-};
 
 // Largest stage count <= smax (looking at most 3 below it) whose largest divisor <= 8 — the
 // number of consumer warps that can stride over the ring — is biggest.
@@ -275,59 +189,7 @@ TmaPlan plan_updown_tma(int B, int H, int I, int dtype) {
   return p;
 }
 
-template <typename T, int BT, int SR, bool XS>
-cudaError_t run_gate_tma_v(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B,
-                           int H, int I, float thr, void* gate_dense, uint8_t* flag_dense,
-                           cudaStream_t st) {
-  return launch(k_gate_tma<T, BT, SR, XS>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
-                (const T*)x, (const T*)Wg, ws, B, H, I, thr, (T*)gate_dense, flag_dense, p.S,
-                p.cw, p.rmax);
-}
-
-template <typename T, int BT>
-cudaError_t run_gate_tma(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B, int H,
-                         int I, float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
-  if (p.sr == 2) {
-    if (p.xs) return run_gate_tma_v<T, BT, 2, true>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
-    return run_gate_tma_v<T, BT, 2, false>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
-  }
-  if (p.xs) return run_gate_tma_v<T, BT, 1, true>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
-  return run_gate_tma_v<T, BT, 1, false>(p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
-}
-
-template <typename T, int BT, int NVT>
-cudaError_t run_updown_tma_nvt(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
-                               WsPtrs ws, int B, int H, int I, void* out, int out_mode,
-                               void* resid, void* x_next, const void* norm_w, float eps,
-                               cudaStream_t st) {
-  if (p.xs)
-    return launch(k_updown_tma<T, BT, NVT, true>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
-                  (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
-                  (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
-  return launch(k_updown_tma<T, BT, NVT, false>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
-                (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
-                (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
-}
-
-template <typename T, int BT>
-cudaError_t run_updown_tma(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
-                           WsPtrs ws, int B, int H, int I, void* out, int out_mode, void* resid,
-                           void* x_next, const void* norm_w, float eps, cudaStream_t st) {
-  switch (p.nvt) {
-    case 1: return run_updown_tma_nvt<T, BT, 1>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
-    case 2: return run_updown_tma_nvt<T, BT, 2>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
-    case 4: return run_updown_tma_nvt<T, BT, 4>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
-    default: return run_updown_tma_nvt<T, BT, 8>(p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next, norm_w, eps, st);
-  }
-}
-
 // ---- persistent kernel ------------------------------------------------------------------------
-struct MegaPlan {
-  bool ok = false;
-  int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0, bulk_flush = 0, mma_dot = 0, parts = kParts;
-  size_t smem = 0;
-};
-
 MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
   MegaPlan p;
   const Options& o = options();
@@ -408,75 +270,12 @@ MegaPlan plan_mega(int L, int B, int H, int I, int dtype, bool has_resid) {
         if (best % d == 0) p.cw = d;
     }
   }
-#ifdef CATS_PHASE_TIMING
-  if (const char* e = getenv("CATS_DEV_S")) {  // development: force the stage count
-    p.S = atoi(e);
-    p.cw = 1;
-    for (int d = 1; d <= kConsumerWarps; ++d)
-      if (p.S % d == 0) p.cw = d;
-  }
-#endif
   if (p.S < 2) return p;
   if (p.S < 8) p.mma_dot = 0;  // a group of eight rows has to fit in the ring
   p.smem = align_up((size_t)p.S * (row_bytes + 16) + 8 * (size_t)(2 * p.S + 3 * kParts + 1), 16) + fixed;
   p.ok = p.smem + statics <= limit;
   return p;
 }
-
-template <typename T, int BT, int NVT>
-cudaError_t launch_mega(const MegaPlan& p, const MegaParams& P, const MegaArgs& A, WsPtrs ws,
-                        cudaStream_t st) {
-  auto kernel = k_cats_mega<T, BT, NVT>;
-  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
-  if (e != cudaSuccess) return e;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(p.grid);
-  cfg.blockDim = dim3(kMegaThreads);
-  cfg.dynamicSmemBytes = p.smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;  // CTAs wait for one another: must be co-resident
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, P, A, ws);
-}
-
-template <typename T, int BT>
-cudaError_t run_mega(const MegaPlan& p, const MegaParams& P, const MegaArgs& A, WsPtrs ws,
-                     cudaStream_t st) {
-  switch (p.nvt) {
-    case 1: return launch_mega<T, BT, 1>(p, P, A, ws, st);
-    case 2: return launch_mega<T, BT, 2>(p, P, A, ws, st);
-    case 4: return launch_mega<T, BT, 4>(p, P, A, ws, st);
-    default: return launch_mega<T, BT, 8>(p, P, A, ws, st);
-  }
-}
-
-// B <= 4 only (the TMA kernels are instantiated for batch tiles 1, 2, 4)
-#ifdef CATS_DEV_HALF_ONLY  // development builds: one instantiation, quick to compile
-#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...) \
-  do { if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__); return FN<__half, 2>(__VA_ARGS__); } while (0)
-#else
-#define CATS_DISPATCH_TMA(dtype, BT_, FN, ...)                                   \
-  do {                                                                           \
-    if ((dtype) == CATS_F32) {                                                   \
-      if (BT_ == 1) return FN<float, 1>(__VA_ARGS__);                            \
-      if (BT_ == 2) return FN<float, 2>(__VA_ARGS__);                            \
-      return FN<float, 4>(__VA_ARGS__);                                          \
-    }                                                                            \
-    if ((dtype) == CATS_F16) {                                                   \
-      if (BT_ == 1) return FN<__half, 1>(__VA_ARGS__);                           \
-      if (BT_ == 2) return FN<__half, 2>(__VA_ARGS__);                           \
-      return FN<__half, 4>(__VA_ARGS__);                                         \
-    }                                                                            \
-    if (BT_ == 1) return FN<__nv_bfloat16, 1>(__VA_ARGS__);                      \
-    if (BT_ == 2) return FN<__nv_bfloat16, 2>(__VA_ARGS__);                      \
-    return FN<__nv_bfloat16, 4>(__VA_ARGS__);                                    \
-  } while (0)
-#endif
 
 cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs ws, int dtype,
                     cudaStream_t st) {
@@ -489,30 +288,14 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
   A.cap = p.cap;
   A.rmax = p.rmax;
-  CATS_DISPATCH_TMA(dtype, batch_tile(A.B), run_mega, p, P, A, ws, st);
-}
-
-cudaError_t do_gate_tma(const TmaPlan& p, const void* x, const void* Wg, WsPtrs ws, int B, int H,
-                        int I, int dtype, float thr, void* gate_dense, uint8_t* flag_dense,
-                        cudaStream_t st) {
-  CATS_DISPATCH_TMA(dtype, batch_tile(B), run_gate_tma, p, x, Wg, ws, B, H, I, thr, gate_dense,
-                    flag_dense, st);
-}
-
-cudaError_t do_updown_tma(const TmaPlan& p, const void* x, const void* Wu, const void* WdT,
-                          WsPtrs ws, int B, int H, int I, int dtype, void* out, int out_mode,
-                          void* resid, void* x_next, const void* norm_w, float eps,
-                          cudaStream_t st) {
-  CATS_DISPATCH_TMA(dtype, batch_tile(B), run_updown_tma, p, x, Wu, WdT, ws, B, H, I, out,
-                    out_mode, resid, x_next, norm_w, eps, st);
+  CATS_DISPATCH(dtype, inst_mega, p, P, A, ws, st);
 }
 
 cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, int dtype,
                     float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
   const TmaPlan p = plan_gate_tma(B, H, I, dtype);
-  if (p.ok) return do_gate_tma(p, x, Wg, ws, B, H, I, dtype, thr, gate_dense, flag_dense, st);
-  CATS_DISPATCH(dtype, batch_tile(B), run_gate, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense,
-                st);
+  if (p.ok) CATS_DISPATCH(dtype, inst_gate_tma, p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
+  CATS_DISPATCH(dtype, inst_gate, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
 }
 
 cudaError_t do_updown(int mode, const void* x, const void* Wu, const void* WdT, WsPtrs ws, int B,
@@ -521,11 +304,11 @@ cudaError_t do_updown(int mode, const void* x, const void* Wu, const void* WdT, 
   if (mode == 3) {
     const TmaPlan p = plan_updown_tma(B, H, I, dtype);
     if (p.ok)
-      return do_updown_tma(p, x, Wu, WdT, ws, B, H, I, dtype, out, out_mode, resid, x_next, norm_w,
-                           eps, st);
+      CATS_DISPATCH(dtype, inst_updown_tma, p, x, Wu, WdT, ws, B, H, I, out, out_mode, resid,
+                    x_next, norm_w, eps, st);
   }
-  CATS_DISPATCH(dtype, batch_tile(B), run_updown, mode, x, Wu, WdT, ws, B, H, I, out, out_mode,
-                resid, x_next, norm_w, eps, inter_dense, st);
+  CATS_DISPATCH(dtype, inst_updown, mode, x, Wu, WdT, ws, B, H, I, out, out_mode, resid, x_next,
+                norm_w, eps, inter_dense, st);
 }
 
 int check_out_mode(int out_mode, const void* out, const void* resid, const void* x_next) {
@@ -897,7 +680,7 @@ int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int 
   if (!aligned16(inter) || !aligned16(Wd)) return CATS_ERR_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto go = [&]() -> cudaError_t {
-    CATS_DISPATCH(dtype, batch_tile(B), run_rows_gemv, inter, Wd, B, I, H, out, st);
+    CATS_DISPATCH(dtype, inst_rows_gemv, inter, Wd, B, I, H, out, st);
   };
   return cuda_status(go());
 }

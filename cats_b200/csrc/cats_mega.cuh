@@ -36,10 +36,6 @@
 
 #include <type_traits>
 
-#ifndef CATS_ONE_FMA_B1
-#define CATS_ONE_FMA_B1 0
-#endif
-
 #include "cats_tma.cuh"
 
 namespace cats {
@@ -305,8 +301,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         tma_load_1d(ring_u + s * row_stride, src, row_bytes, full_u + 8u * s);
       };
       for (int l = 0; l < L && ok; ++l) {
-        const bool tl = (l == L / 2) && p == 0;
-        CATS_STAMP(1, 0, tl);
         const T* Wg = reinterpret_cast<const T*>(P.wg[l]);
         const T* Wu = reinterpret_cast<const T*>(P.wu[l]);
         const T* Wd = reinterpret_cast<const T*>(P.wdt[l]);
@@ -314,39 +308,24 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
           // own items only: j == (p - k) mod npw, stepping by npw (no division per row)
           for (int j = ((p - k) % npw + npw) % npw; j < R && ok; j += npw) {
-#ifdef CATS_PHASE_TIMING
-            if ((l == L / 2) && h == 1 && c == 5 && j < 64) cats_trace[4][j] = cats_now();
-#endif
             issue(k + j, Wg + (size_t)(r0 + j) * H);
-#ifdef CATS_PHASE_TIMING
-            if ((l == L / 2) && h == 1 && c == 5 && j < 64) cats_trace[5][j] = cats_now();
-#endif
           }
           k += R;
-          CATS_STAMP(1, 1 + h, tl && h < 2);
         }
         for (int h = 0; h < NP && ok; ++h) {
           if (!mbar_wait(lready_u + 8u * h, l & 1, &s_abort)) {
             ok = false;
             break;
           }
-          CATS_STAMP(1, 3 + 2 * h, tl && h < 2);
           const int cnt = s_cnt[h];
           const int* idx = s_idx + h * A.cap;
           for (int j = ((p - k) % npw + npw) % npw; j < cnt && ok; j += npw)
             issue(k + j, Wu + (size_t)idx[j] * H);
           k += cnt;
           for (int j = ((p - k) % npw + npw) % npw; j < cnt && ok; j += npw) {
-#ifdef CATS_PHASE_TIMING
-            if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[2][j] = cats_now();
-#endif
             issue(k + j, Wd + (size_t)idx[j] * H);
-#ifdef CATS_PHASE_TIMING
-            if ((l == L / 2) && h == 0 && c == 5 && j < 32) cats_trace[3][j] = cats_now();
-#endif
           }
           k += cnt;
-          CATS_STAMP(1, 4 + 2 * h, tl && h < 2);
         }
       }
     }
@@ -358,11 +337,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     for (int l = 0; l < L; ++l) {
       const float thr = P.thr[l];
       for (int h = 0; h < NP; ++h) {
-        const bool tl = (l == L / 2) && lane == 0;
         // this CTA's gate values of part h are in: ballot / popc compaction, publish, arrive
         if (ok) ok = mbar_wait(gdone_u + 8u * h, l & 1, &s_abort);
         ok = __all_sync(0xffffffffu, ok);
-        CATS_STAMP(2, 4 + 5 * h, tl && h < 2);
         if (ok) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
           const float* sv = s_val + (size_t)h * A.rmax * BT;
@@ -396,12 +373,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           // complete (and fenced) before this CTA lets the barrier of (l, 0) complete
           if (h == 0 && l >= 2 && !K) ok = mbar_wait(zdone_u, (l - 2) & 1, &s_abort);
           ok = __all_sync(0xffffffffu, ok);
-          CATS_STAMP(2, 0 + 5 * h, tl && h < 2);
           __syncwarp();
           if (lane == 0 && ok) grid_arrive(gbar + h);
-          CATS_STAMP(2, 1 + 5 * h, tl && h < 2);
         }
-        CATS_STAMP(1, 8 + 3 * h, tl && h < 2);
       }
     }
   } else if (warp == kConsumerWarps + kMegaProducers + 1) {
@@ -409,11 +383,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     bool ok = true;
     for (int l = 0; l < L; ++l) {
       for (int h = 0; h < NP; ++h) {
-        const bool tl = (l == L / 2) && lane == 0;
         // all CTAs have published part h: scan the counts, take this CTA's balanced share
         if (ok) ok = grid_wait(gbar + h, gtarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
-        CATS_STAMP(1, 9 + 3 * h, tl && h < 2);
         const int* cntp = ws.seg_count + h * kSegHalfStride;
         int cv[kMegaMaxGrid / 32];
 #pragma unroll
@@ -437,7 +409,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           run += __shfl_sync(0xffffffffu, v, 31);
         }
         __syncwarp();
-        CATS_STAMP(2, 2 + 5 * h, tl && h < 2);
         const int n = run;
         const int p0 = (int)(((long long)c * n) / G), p1 = (int)(((long long)(c + 1) * n) / G);
         const int cnt = ok ? p1 - p0 : 0;
@@ -465,7 +436,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         }
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(lready_u + 8u * h);
-        CATS_STAMP(1, 10 + 3 * h, tl && h < 2);
       }
       if (K) {
         // Tensor parallel: once every CTA of this GPU has added its share of layer l, send this
@@ -533,7 +503,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (tid == 0 && ok) grid_wait(obar, otarget(l), &s_abort);
       }
       consumer_bar_sync();
-      CATS_STAMP(0, 4, (l + 1 == L / 2) && tid == 0);
       ok = !s_abort;
       const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
       const uint2* slots = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H) : nullptr;
@@ -624,7 +593,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
           }
         }
-        CATS_STAMP(0, 5, (l + 1 == L / 2) && tid == 0 && b == 0);
         if (has_resid) {
           ss = warp_sum(ss);
           consumer_bar_sync();
@@ -704,10 +672,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     };
 
     for (int l = 0; l < L; ++l) {
-      const bool tl = (l == L / 2);
-      CATS_STAMP(0, 0, tl && tid == 0);
       if (l > 0) next_x(l - 1, false);
-      CATS_STAMP(0, 1, tl && tid == 0);
       const float thr = P.thr[l];
 #pragma unroll
       for (int g = 0; g < NVT; ++g)
@@ -737,9 +702,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           for (; j < R && ok; j += cw) {
             const int kk = k + j, cy = cyc_of(kk), s = kk - cy * S;
             if (!(ok = mbar_wait_warp(full_u + 8u * s, cy & 1, &s_abort))) break;
-#ifdef CATS_PHASE_TIMING
-            if (tl && h == 1 && c == 5 && lane == 0 && j < 64) cats_trace[6][j] = cats_now();
-#endif
             float a1[BT];
             warp_dot1_smem<T, BT>(reinterpret_cast<const T*>(ring + (size_t)s * row_stride), xs, B,
                                   H, lane, a1, xs_ld);
@@ -750,22 +712,16 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_n(empty_u + 8u * s, kConsumerWarps);
-#ifdef CATS_PHASE_TIMING
-            if (tl && h == 1 && c == 5 && lane == 0 && j < 64) cats_trace[7][j] = cats_now();
-#endif
           }
         }
         k += R;
         __syncwarp();
-        CATS_STAMP(0, 2 + h, tl && tid == 0 && h < 2);
         if (lane == 0) mbar_arrive(gdone_u + 8u * h);
       }
 
       // ---- up and down rows of the two halves ----------------------------------------------------
       for (int h = 0; h < NP; ++h) {
-        CATS_STAMP(0, 6 + 4 * h, tl && tid == 0 && h < 2);
         if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
-        CATS_STAMP(0, 7 + 4 * h, tl && tid == 0 && h < 2);
         if (mma_dot) {  // the group loop below needs the same trip count in every warp
           consumer_bar_sync();
           ok = !s_abort;
@@ -798,22 +754,15 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           }
         }
         k += cnt;
-        CATS_STAMP(0, 8 + 4 * h, tl && tid == 0 && h < 2);
         consumer_bar_sync();  // every h_j of this half is final; all earlier items are consumed
         ok = !s_abort;
         // Down rows in groups of kDG: lane q waits for the q-th row of the group (one round trip
         // to the barrier unit for the whole group instead of one per row), the warp adds the
         // group's rows, then lane q releases the q-th stage.
         constexpr int kDG = 8;
-#ifdef CATS_PHASE_TIMING
-        long long dbg_w = 0, dbg_p = 0, dbg_a = 0, dbg_t;
-#endif
         const int dg = min(kDG, S);  // a group must fit in the ring
         for (int j0 = 0; j0 < cnt && ok; j0 += dg) {
           const int nb = min(dg, cnt - j0);
-#ifdef CATS_PHASE_TIMING
-          dbg_t = clock64();
-#endif
           bool mine = true;
           if (lane < nb) {
             const int kk = k + j0 + lane;
@@ -822,15 +771,10 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           }
           ok = __all_sync(0xffffffffu, mine);
           if (!ok) break;
-#ifdef CATS_PHASE_TIMING
-          dbg_w += clock64() - dbg_t; dbg_t = clock64();
-          if (tl && h == 0 && c == 5 && tid == 0 && j0 < 32) cats_trace[0][j0] = cats_now();
-          if (tl && h == 0 && c == 5 && tid == 224 && j0 < 32) cats_trace[1][j0] = cats_now();
-#endif
           // all loads of a column group first (kDG independent 16-byte loads in flight per
           // thread), then the FMAs: with two warps per scheduler nothing else hides the latency
           // batches: the scalar rounded to the storage type, one FMA per weight (prep1 / axpy1)
-          constexpr bool kOneFma = (BT >= 2 || CATS_ONE_FMA_B1) && sizeof(T) == 2;
+          constexpr bool kOneFma = BT >= 2 && sizeof(T) == 2;
           typedef typename std::conditional<kOneFma, uint32_t, typename V::Scalar>::type HScalar;
           HScalar hb[kDG][BT];
           const uint4* rowp[kDG];
@@ -860,27 +804,16 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
           }
           __syncwarp();
-#ifdef CATS_PHASE_TIMING
-          dbg_p += clock64() - dbg_t; dbg_t = clock64();
-#endif
           if (lane < nb) {
             const int kk = k + j0 + lane;
             mbar_arrive(empty_u + 8u * slot_of(kk));
           }
-#ifdef CATS_PHASE_TIMING
-          dbg_a += clock64() - dbg_t;
-#endif
         }
-#ifdef CATS_PHASE_TIMING
-        if (tl && h == 0 && c == 5 && lane == 0) { cats_trace[1][32 + warp * 3] = dbg_w; cats_trace[1][33 + warp * 3] = dbg_p; cats_trace[1][34 + warp * 3] = dbg_a; }
-#endif
         k += cnt;
         __syncwarp();
-        CATS_STAMP(0, 9 + 4 * h, tl && tid == 0 && h < 2);
         if (lane == 0 && ok) mbar_arrive(lfree_u + 8u * h);
       }
 
-      CATS_STAMP(0, 15, tl && tid == 0);
       // ---- this CTA's share of the down projection into the layer's fp32 accumulators ----------
       if (ok && A.bulk_flush) {
         // Through shared memory: a warp's 32 vectors of one (g, t) are 32 * N contiguous
@@ -940,7 +873,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       // every warp publishes its own share of the sums: no CTA barrier, one fence per warp
       __syncwarp();
       if (lane == 0 && ok) grid_arrive(obar);
-      CATS_STAMP(0, 14, tl && tid == 0);
     }
 
     next_x(L - 1, true);

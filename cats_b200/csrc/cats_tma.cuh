@@ -32,25 +32,6 @@ constexpr long long kWaitCycles = 2000000000LL;     // ~1 s at B200 clocks
 
 enum { STATUS_OK = 0, STATUS_WAIT_TIMEOUT_GATE = 1, STATUS_WAIT_TIMEOUT_UPDOWN = 2 };
 
-// Optional per-CTA phase timestamps for development builds (compiled out by default).
-#ifdef CATS_PHASE_TIMING
-__device__ unsigned long long cats_stamps[3][256][16];
-__device__ unsigned long long cats_trace[8][64];  // per-item times of one CTA (development)
-__device__ __forceinline__ unsigned long long cats_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-// predicated store, no branch: a stamp must not make the calling warp diverge
-__device__ __forceinline__ void cats_stamp(int kernel, int slot, bool cond) {
-  unsigned long long* p = &cats_stamps[kernel][blockIdx.x][slot];
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .u64 t;\n\tsetp.ne.u32 p, %1, 0;\n\t"
-      "mov.u64 t, %globaltimer;\n\t@p st.global.u64 [%0], t;\n\t}" ::"l"(p),
-      "r"((unsigned)cond)
-      : "memory");
-}
-#define CATS_STAMP(kernel, slot, cond) cats_stamp(kernel, slot, cond)
-#else
-#define CATS_STAMP(kernel, slot, cond) do { } while (0)
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -324,7 +305,6 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
     tma_load_1d(ring_u + s * stage_bytes, src + (size_t)k * stage_bytes, bytes, full_u + 8u * s);
   };
 
-  CATS_STAMP(0, 0, tid == 0);
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full_u + 8u * s, 1);
@@ -340,15 +320,12 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
   int k_issued = pw;
   if (pw >= 0 && lane == 0)
     for (; k_issued < nst && k_issued < S; k_issued += npw) issue(k_issued);
-  CATS_STAMP(0, 1, tid == 0);
   pdl_wait();
   pdl_launch_dependents();
-  CATS_STAMP(0, 2, tid == 0);
   if (XS) {
     stage_x<T>(x, xs, B, H);
     __syncthreads();
   }
-  CATS_STAMP(0, 3, tid == 0);
   const T* xsrc = XS ? xs : x;
 
   if (warp >= kConsumerWarps) {
@@ -388,10 +365,7 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
       if (lane == 0) mbar_arrive(empty_u + 8u * s);
     }
   }
-  CATS_STAMP(0, 4, tid == 0);
-  CATS_STAMP(0, 5, tid == kConsumerThreads);
   __syncthreads();
-  CATS_STAMP(0, 6, tid == 0);
   if (s_abort) {
     if (tid == 0) atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_GATE);
     drain_after_abort();
@@ -430,7 +404,6 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
       ws.seg_count[c] = base;
       if (c == 0) ws.hdr[HDR_NSEG] = nseg;
     }
-    CATS_STAMP(0, 7, lane == 0);
   }
 }
 
@@ -474,7 +447,6 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
   const int G = gridDim.x, c = blockIdx.x;
   const int nvec = H / N;
 
-  CATS_STAMP(1, 0, tid == 0);
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full_u + 8u * s, 1);
@@ -490,7 +462,6 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
 
   pdl_wait();
   pdl_launch_dependents();
-  CATS_STAMP(1, 1, tid == 0);
 
   int nseg;
   const int n = scan_segments(ws.seg_count, ws.hdr + HDR_NSEG, &nseg, s_incl, s_part);
@@ -505,7 +476,6 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
       s_h[j * BT + t] = (t < B) ? __ldcg(ws.seg_gate + (size_t)q * B + t) : 0.f;
   }
   __syncthreads();
-  CATS_STAMP(1, 2, tid == 0);
   const T* xsrc = XS ? xs : x;
 
   const int nitems = 2 * cnt;
@@ -539,9 +509,7 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
       __syncwarp();
       if (lane == 0) mbar_arrive_n(empty_u + 8u * s, kConsumerWarps);
     }
-    CATS_STAMP(1, 3, tid == 0);
     consumer_bar_sync();  // every h_j of this CTA is final
-    CATS_STAMP(1, 4, tid == 0);
     ok = ok && !s_abort;
     // down rows
     float acc[NVT][N][BT];
@@ -575,7 +543,6 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_u + 8u * s);
     }
-    CATS_STAMP(1, 5, tid == 0);
     if (cnt > 0) {
 #pragma unroll
       for (int g = 0; g < NVT; ++g) {
@@ -597,10 +564,8 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
   }
 
   // completion ticket: the CTA that arrives last owns the epilogue
-  CATS_STAMP(1, 6, tid == 0);
   __threadfence();
   __syncthreads();
-  CATS_STAMP(1, 7, tid == 0);
   if (s_abort) {
     if (tid == 0) atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_UPDOWN);
     drain_after_abort();
@@ -610,12 +575,10 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
     s_last = (t == (unsigned)G - 1u) ? 1 : 0;
   }
   __syncthreads();
-  CATS_STAMP(1, 8, tid == 0);
   if (s_last) {
     __threadfence();
     finalize_down<T>(ws, B, H, out, out_mode, resid, x_next, norm_w, eps, s_red);
     if (tid == 0) ws.hdr[HDR_TICKET] = 0;
-    CATS_STAMP(1, 9, tid == 0);
   }
 }
 
