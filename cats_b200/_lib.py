@@ -50,6 +50,7 @@ SIGNATURES = {
     "cats_mlp_static": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_void_p, _c_void_p]),
     "cats_mlp_static_limit": (_c_size_t, []),
+    "cats_mlp_static_status": (_c_int, [ctypes.POINTER(_c_int), _c_void_p]),
     "cats_mlp_stack": (_c_int, [_c_int, ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                 ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_float), _c_void_p,
                                 _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,

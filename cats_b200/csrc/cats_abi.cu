@@ -22,10 +22,12 @@ const DevInfo& dev_info() {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
   if (info[dev].sms == 0) {
-    int sms = 0, smem = 0;
+    int sms = 0, smem = 0, khz = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
     info[dev].max_smem_optin = smem;
+    info[dev].clock_khz = khz > 0 ? khz : 1965000;
     info[dev].sms = sms > 0 ? sms : 148;
   }
   return info[dev];
@@ -101,6 +103,7 @@ struct Options {
   int bulk_flush = 1;  // persistent kernel: flush accumulators with TMA bulk reduces
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
+  int wait_ms = 1000;  // limit of every device-side wait (mbarrier, grid barrier, peer data)
 };
 Options& options() {
   static Options o = [] {
@@ -112,9 +115,19 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_BULK_FLUSH")) v.bulk_flush = atoi(e);
     if (const char* e = getenv("CATS_B200_MMA_DOT")) v.mma_dot = atoi(e);
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
+    if (const char* e = getenv("CATS_B200_WAIT_MS")) v.wait_ms = atoi(e);
     return v;
   }();
   return o;
+}
+
+// The wait limit in units of 1024 clock cycles of the current device.
+int wait_kcycles() {
+  long long ms = options().wait_ms;
+  if (ms < 1) ms = 1;
+  if (ms > 60000) ms = 60000;
+  const long long kc = ms * dev_info().clock_khz / 1024;
+  return (int)(kc > 0x7fffffffLL ? 0x7fffffffLL : kc);
 }
 
 // Largest stage count <= smax (looking at most 3 below it) whose largest divisor <= 8 — the
@@ -155,6 +168,7 @@ TmaPlan plan_gate_tma(int B, int H, int I, int dtype) {
   p.rmax = (I + p.grid - 1) / p.grid;
   p.smem = align_up(p.S * stage + 16 * (size_t)p.S + 4 * (size_t)p.rmax * batch_tile(B), 16) +
            (p.xs ? xbytes : 0);
+  p.wait_kc = wait_kcycles();
   p.ok = p.smem + 2048 <= (size_t)dev_info().max_smem_optin;
   return p;
 }
@@ -185,6 +199,7 @@ TmaPlan plan_updown_tma(int B, int H, int I, int dtype) {
   p.smem = align_up(p.S * row_bytes + 16 * (size_t)p.S +
                         4 * (size_t)p.cap * (1 + batch_tile(B)), 16) +
            (p.xs ? xbytes : 0);
+  p.wait_kc = wait_kcycles();
   p.ok = p.smem + 8192 <= (size_t)dev_info().max_smem_optin;
   return p;
 }
@@ -285,6 +300,7 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   A.bulk_flush = p.bulk_flush;
   A.mma_dot = p.mma_dot;
   A.parts = p.parts;
+  A.wait_kc = wait_kcycles();
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
   A.cap = p.cap;
   A.rmax = p.rmax;
@@ -358,6 +374,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "bulk_flush")) options().bulk_flush = value;
   else if (!strcmp(name, "mma_dot")) options().mma_dot = value;
   else if (!strcmp(name, "parts")) options().parts = value;
+  else if (!strcmp(name, "wait_ms")) options().wait_ms = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }
@@ -660,15 +677,23 @@ int cats_mlp_static(const void* x, const void* Wg, const void* Wu, const void* W
   ws_layout(base, H, I, &p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The array still holds whatever the previous call (of any caller) left in it.  What the
-  // kernels need to find zero is cleared here, in stream order: the header (completion ticket,
-  // status word) and the fp32 accumulators of the B tokens.
-  cudaError_t e = cudaMemsetAsync(p.hdr, 0, sizeof(int) * kHdrInts, st);
+  // kernels need to find zero is cleared here, in stream order: the completion ticket and the
+  // fp32 accumulators of the B tokens.  The sticky status word is left alone.
+  cudaError_t e = cudaMemsetAsync(p.hdr + HDR_TICKET, 0, sizeof(int), st);
   if (e == cudaSuccess) e = cudaMemsetAsync(p.acc32, 0, sizeof(float) * (size_t)B * H, st);
   if (e != cudaSuccess) return cuda_status(e);
   e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, CATS_OUT_STORE, nullptr,
                                nullptr, nullptr, 0.f, nullptr, st));
+}
+
+int cats_mlp_static_status(int* device_status, void* stream) {
+  if (!device_status) return CATS_ERR_NULL;
+  void* base = nullptr;
+  int s = static_ws_for_current_device(&base);
+  if (s) return s;
+  return cats_read_counters(base, nullptr, device_status, stream);
 }
 
 int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int dtype, void* out,

@@ -57,7 +57,7 @@ cudaError_t run_gate_tma_v(const TmaPlan& p, const void* x, const void* Wg, WsPt
                            cudaStream_t st) {
   return launch(k_gate_tma<T, BT, SR, XS>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
                 (const T*)x, (const T*)Wg, ws, B, H, I, thr, (T*)gate_dense, flag_dense, p.S,
-                p.cw, p.rmax);
+                p.cw, p.rmax, p.wait_kc);
 }
 
 template <typename T, int BT>
@@ -79,10 +79,10 @@ cudaError_t run_updown_tma_nvt(const TmaPlan& p, const void* x, const void* Wu, 
   if (p.xs)
     return launch(k_updown_tma<T, BT, NVT, true>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
                   (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
-                  (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
+                  (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw, p.wait_kc);
   return launch(k_updown_tma<T, BT, NVT, false>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
                 (const T*)x, (const T*)Wu, (const T*)WdT, ws, B, H, I, p.cap, (T*)out, out_mode,
-                (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw);
+                (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S, p.cw, p.wait_kc);
 }
 
 template <typename T, int BT>

@@ -74,6 +74,7 @@ struct MegaArgs {
   int npw;               // producer threads in use (divides S)
   int bulk_flush;        // 1: accumulators leave through shared memory and TMA bulk reduces
   int mma_dot;           // 1: gate / up dot products of eight rows at a time on the tensor cores
+  int wait_kc;           // limit of every wait, in units of 1024 clock cycles
   int parts;             // parts per layer (1..kParts): more parts hide the list latency behind
                          // other parts' rows, fewer parts mean fewer grid barriers per layer
   unsigned s_magic;      // floor(2^32 / S) + 1: item -> (ring cycle, slot) without a division
@@ -89,22 +90,27 @@ struct MegaArgs {
   unsigned char* xchg[kMaxRanks];
 };
 
-// Exchange buffer of one rank (see MegaArgs::xchg).  Header: one arrival counter per SOURCE rank
-// (a source's CTAs bump it once per layer after their stores into this buffer — a hint that
-// the data is probably there, not a guarantee), the counters' common value at the start of the
-// current launch, and the running number of layers (its low bit selects the slot set, so
-// consecutive layers alternate sets across launches too; plus one it is the tag of the layer's
-// data).  Then slots[2][kMaxRanks][kMegaMaxB * H] of 8-byte (value, tag) pairs: slots[s][p] =
-// rank p's partial sums.  A pair is written with one store, so a reader that finds the tag it
-// expects has the value that belongs to it: no fence orders data against flags, on either side.
-enum { XCH_ARRIVED = 0 /* [kMaxRanks] */, XCH_BASE = 16, XCH_LAYERS = 17, XCH_HDR_BYTES = 256 };
+// Exchange buffer of one rank (see MegaArgs::xchg).  Header: the running number of layers (its
+// low bit selects the slot set, so consecutive layers alternate sets across launches too; plus
+// one it is the tag of the layer's data).  Then slots[2][kMaxRanks][kMegaMaxB * H] of 8-byte
+// (value, tag) pairs, slots[s][p] = rank p's partial sums as stored by rank p's CTAs over NVLink,
+// and sums[2][kMegaMaxB * H] pairs, the ranks' total as written by this GPU's own CTAs.
+// A pair is ONE 64-bit element of every store and load that touches it (st / ld ... .v2.b64:
+// two pairs per instruction, each element single-copy atomic in the PTX memory model), so a
+// reader that finds the tag it expects has the value that belongs to it: no fence and no flag
+// orders data against anything, on either side; a pair that has not arrived is read again.
+enum { XCH_LAYERS = 0, XCH_HDR_BYTES = 256 };
 constexpr int kMegaMaxB = 4;
 __host__ __device__ inline size_t xchg_bytes(int H) {
-  return XCH_HDR_BYTES + sizeof(uint2) * 2 * (size_t)kMaxRanks * kMegaMaxB * H;
+  return XCH_HDR_BYTES + sizeof(uint2) * 2 * (size_t)(kMaxRanks + 1) * kMegaMaxB * H;
 }
 __host__ __device__ inline uint2* xchg_slot(unsigned char* base, int set, int src, int H) {
   return reinterpret_cast<uint2*>(base + XCH_HDR_BYTES) +
          ((size_t)set * kMaxRanks + src) * kMegaMaxB * H;
+}
+__host__ __device__ inline uint2* xchg_sums(unsigned char* base, int set, int H) {
+  return reinterpret_cast<uint2*>(base + XCH_HDR_BYTES) +
+         ((size_t)2 * kMaxRanks + set) * kMegaMaxB * H;
 }
 
 // Rows [lo, hi) of half h out of I.
@@ -138,44 +144,49 @@ __device__ __forceinline__ bool grid_wait(const unsigned* ctr, unsigned target,
       __nanosleep(40);
     }
     if (*abort) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > wait_limit(abort)) {
       *abort = 1;
       return false;
     }
   }
 }
 
-// The same pair at system scope, for counters that other GPUs add to over NVLink (the counter
-// polled is always in this GPU's own memory).  Other ranks' kernels are launched by other
-// processes, so the bound is several times the local one.
-__device__ __forceinline__ void peer_arrive(unsigned* ctr) {  // a hint: see the exchange buffer
-  asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+// Two (value, tag) pairs = 16 bytes, each pair one 64-bit element.  System scope: the slots are
+// written by other GPUs over NVLink (and read from this GPU's own memory); the sums are local
+// but share the code.
+__device__ __forceinline__ unsigned long long make_pair(float v, unsigned tag) {
+  return (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
 }
-__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
+__device__ __forceinline__ void st_pairs(uint2* p, unsigned long long a, unsigned long long b) {
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void ld_pairs(const uint2* p, unsigned long long& a,
+                                         unsigned long long& b) {
+  asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
-__device__ __forceinline__ bool peer_wait(const unsigned* ctr, unsigned target,
-                                          volatile int* abort) {
-  if ((int)(ld_acquire_sys(ctr) - target) >= 0) return true;
+__device__ __forceinline__ bool pair_has(unsigned long long a, unsigned tag) {
+  return (unsigned)(a >> 32) == tag;
+}
+__device__ __forceinline__ float pair_val(unsigned long long a) {
+  return __uint_as_float((unsigned)a);
+}
+// Four consecutive pairs (one group of four columns) with the tag `tag`, re-read until every one
+// of them has arrived; bounded like every wait.  False when the limit ran out.
+__device__ __forceinline__ bool ld_group_tagged(const uint2* p, unsigned tag, volatile int* abort,
+                                                unsigned long long (&u)[4]) {
+  ld_pairs(p, u[0], u[1]);
+  ld_pairs(p + 2, u[2], u[3]);
+  if (pair_has(u[0], tag) && pair_has(u[1], tag) && pair_has(u[2], tag) && pair_has(u[3], tag))
+    return true;
   const long long t0 = clock64();
   for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-      if ((int)(ld_acquire_sys(ctr) - target) >= 0) return true;
-      __nanosleep(40);
-    }
+    __nanosleep(64);
+    ld_pairs(p, u[0], u[1]);
+    ld_pairs(p + 2, u[2], u[3]);
+    if (pair_has(u[0], tag) && pair_has(u[1], tag) && pair_has(u[2], tag) && pair_has(u[3], tag))
+      return true;
     if (*abort) return false;
-    if (clock64() - t0 > 4 * kWaitCycles) {
+    if (clock64() - t0 > 4 * wait_limit(abort)) {  // other ranks are launched by other processes
       *abort = 1;
       return false;
     }
@@ -188,7 +199,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   using V = VecT<T>;
   constexpr int N = V::N;
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_abort;
+  __shared__ int s_ctl[2];  // abort flag, wait limit
+  int& s_abort = s_ctl[0];
   __shared__ float s_red[32];
   __shared__ int s_cnt[kParts];
   __shared__ int s_pref[kMegaMaxGrid];
@@ -248,7 +260,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   // tensor-parallel exchange (K == 0: single GPU)
   const int K = A.nranks;
   unsigned* xflag = K ? reinterpret_cast<unsigned*>(A.xchg[A.rank]) : nullptr;
-  const unsigned xbase = K ? __ldcg(xflag + XCH_BASE) : 0u;
   const unsigned xl0 = K ? __ldcg(xflag + XCH_LAYERS) : 0u;
   // this CTA's slice (groups of 4 columns) of a [B, H] vector
   const int ngrp_all = H >> 2;
@@ -267,6 +278,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     }
     mbar_init(zdone_u, 1);
     s_abort = 0;
+    s_ctl[1] = A.wait_kc;
     mbar_fence_init();
   }
   for (int b = 0; b < B; ++b)
@@ -439,34 +451,52 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       }
       if (K) {
         // Tensor parallel: once every CTA of this GPU has added its share of layer l, send this
-        // CTA's slice of the sums to every rank's slot for this rank (plain stores of
-        // (value, tag) pairs into peer memory, then a relaxed bump of the hint counters), and
-        // clear the slice for layer l+2 (nobody else reads the accumulators in this mode; the
-        // clearing reaches the other CTAs through the list and layer barriers of layer l+1).
+        // CTA's slice of the sums to every rank's slot for this rank (plain stores of (value,
+        // tag) pairs into peer memory) and clear the slice for layer l+2 (nobody else reads the
+        // accumulators in this mode; the clearing reaches the other CTAs through the list and
+        // layer barriers of layer l+1).  Then add the ranks' partial sums of the same slice as
+        // they arrive in this GPU's slots - in rank order, so every rank computes bit-identical
+        // totals - and publish the total, tagged again, for all CTAs of this GPU: a CTA reads
+        // B * H totals per layer instead of nranks * B * H partial sums.
         if (ok) ok = grid_wait(obar, otarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
           const int set = (int)((xl0 + (unsigned)l) & 1u);
           const unsigned tag = xl0 + (unsigned)l + 1u;
-          for (int b = 0; b < B; ++b) {
-            for (int g = own_lo + lane; g < own_hi; g += 32) {
-              float4* src = reinterpret_cast<float4*>(accp + (size_t)b * H) + g;
-              const float4 v = __ldcg(src);
-              *src = make_float4(0.f, 0.f, 0.f, 0.f);
-              const uint4 lo4 = make_uint4(__float_as_uint(v.x), tag, __float_as_uint(v.y), tag);
-              const uint4 hi4 = make_uint4(__float_as_uint(v.z), tag, __float_as_uint(v.w), tag);
-              for (int p = 0; p < K; ++p) {
-                uint4* dst = reinterpret_cast<uint4*>(xchg_slot(A.xchg[p], set, A.rank, H) +
-                                                      (size_t)b * H + 4 * (size_t)g);
-                dst[0] = lo4;
-                dst[1] = hi4;
-              }
+          const int own_n = own_hi - own_lo;
+          for (int e = lane; e < B * own_n; e += 32) {
+            const int b = e / own_n, g = own_lo + (e - b * own_n);
+            float4* src = reinterpret_cast<float4*>(accp + (size_t)b * H) + g;
+            const float4 v = __ldcg(src);
+            *src = make_float4(0.f, 0.f, 0.f, 0.f);
+            const unsigned long long q0 = make_pair(v.x, tag), q1 = make_pair(v.y, tag),
+                                     q2 = make_pair(v.z, tag), q3 = make_pair(v.w, tag);
+            for (int p = 0; p < K; ++p) {
+              uint2* dst = xchg_slot(A.xchg[p], set, A.rank, H) + (size_t)b * H + 4 * (size_t)g;
+              st_pairs(dst, q0, q1);
+              st_pairs(dst + 2, q2, q3);
             }
           }
-          __syncwarp();
-          if (lane < K)
-            peer_arrive(reinterpret_cast<unsigned*>(A.xchg[lane]) + XCH_ARRIVED + A.rank);
+          bool good = true;
+          for (int e = lane; e < B * own_n; e += 32) {
+            const int b = e / own_n, g = own_lo + (e - b * own_n);
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < K && good; ++p) {
+              unsigned long long u[4];
+              good = ld_group_tagged(xchg_slot(A.xchg[A.rank], set, p, H) + (size_t)b * H +
+                                         4 * (size_t)g, tag, &s_abort, u);
+              a.x += pair_val(u[0]); a.y += pair_val(u[1]);
+              a.z += pair_val(u[2]); a.w += pair_val(u[3]);
+            }
+            if (good) {
+              uint2* dst = xchg_sums(A.xchg[A.rank], set, H) + (size_t)b * H + 4 * (size_t)g;
+              st_pairs(dst, make_pair(a.x, tag), make_pair(a.y, tag));
+              st_pairs(dst + 2, make_pair(a.z, tag), make_pair(a.w, tag));
+            }
+          }
+          ok = __all_sync(0xffffffffu, good);
+          __threadfence();  // the cleared slice, ahead of this warp's next barrier hand-offs
         }
       } else if (l >= 1) {
         // Every CTA has read layer l-1's accumulators (it needed x_l for gate rows that are
@@ -494,20 +524,15 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // computes the whole vector for itself; global outputs are written in disjoint slices.
     auto next_x = [&](int l, bool last) {
       // single GPU: all CTAs' sums are in the accumulators once the layer barrier completes;
-      // tensor parallel: every rank's partial sums are (most probably) in this GPU's slots once
-      // every source rank's G CTAs have bumped their counter (thread p polls source p's); the
-      // tags of the pairs decide
-      if (K) {
-        if (tid < K && ok) peer_wait(xflag + XCH_ARRIVED + tid, xbase + (unsigned)(l + 1) * G, &s_abort);
-      } else {
+      // tensor parallel: the ranks' totals arrive slice by slice as tagged pairs (see the lister)
+      if (!K) {
         if (tid == 0 && ok) grid_wait(obar, otarget(l), &s_abort);
       }
       consumer_bar_sync();
       ok = !s_abort;
       const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
-      const uint2* slots = K ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H) : nullptr;
+      const uint2* sums = K ? xchg_sums(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), H) : nullptr;
       const unsigned tag = xl0 + (unsigned)l + 1u;
-      const size_t src_stride = (size_t)kMegaMaxB * H;  // pairs between source ranks' slots
       const int ngrp = ngrp_all;
       const T* nw = reinterpret_cast<const T*>(P.nw[l]);
       constexpr int KV = 4;
@@ -523,49 +548,31 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
                                 : make_float4(0.f, 0.f, 0.f, 0.f);
             }
           } else {
-            // The ranks' partial sums, added in rank order on every GPU (identical x everywhere),
-            // two sources' loads in flight at a time.  Every pair carries the layer's tag: a
-            // pair that has not arrived yet (the counters are only a hint) is simply read again.
+            // all loads first (one L2 round trip when everything has arrived), then the checks;
+            // a group whose pairs are not all there yet is read again on its own
+            unsigned long long u[KV][4];
 #pragma unroll
-            for (int q = 0; q < KV; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int p0 = 0; p0 < K && ok; p0 += 2) {
-              uint4 u[2][KV][2];
-              const long long t0 = clock64();
-              for (;;) {
-                bool good = true;
-#pragma unroll
-                for (int pp = 0; pp < 2; ++pp)
-#pragma unroll
-                  for (int q = 0; q < KV; ++q) {
-                    const int g = g0 + q * kConsumerThreads + tid;
-                    if (p0 + pp < K && g < ngrp) {
-                      const uint2* src = slots + (size_t)(p0 + pp) * src_stride + (size_t)b * H + 4 * (size_t)g;
-                      u[pp][q][0] = ld_volatile_v4(src);
-                      u[pp][q][1] = ld_volatile_v4(src + 2);
-                    } else {
-                      u[pp][q][0] = u[pp][q][1] = make_uint4(0u, tag, 0u, tag);
-                    }
-                  }
-#pragma unroll
-                for (int pp = 0; pp < 2; ++pp)
-#pragma unroll
-                  for (int q = 0; q < KV; ++q)
-                    good = good && u[pp][q][0].y == tag && u[pp][q][0].w == tag &&
-                           u[pp][q][1].y == tag && u[pp][q][1].w == tag;
-                if (good) break;
-                if (s_abort || clock64() - t0 > 4 * kWaitCycles) {
-                  s_abort = 1;
-                  ok = false;
-                  break;
-                }
+            for (int q = 0; q < KV; ++q) {
+              const int g = g0 + q * kConsumerThreads + tid;
+              if (g < ngrp) {
+                const uint2* src = sums + (size_t)b * H + 4 * (size_t)g;
+                ld_pairs(src, u[q][0], u[q][1]);
+                ld_pairs(src + 2, u[q][2], u[q][3]);
               }
+            }
 #pragma unroll
-              for (int pp = 0; pp < 2; ++pp)
-#pragma unroll
-                for (int q = 0; q < KV; ++q) {
-                  a[q].x += __uint_as_float(u[pp][q][0].x); a[q].y += __uint_as_float(u[pp][q][0].z);
-                  a[q].z += __uint_as_float(u[pp][q][1].x); a[q].w += __uint_as_float(u[pp][q][1].z);
-                }
+            for (int q = 0; q < KV; ++q) {
+              const int g = g0 + q * kConsumerThreads + tid;
+              a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (g < ngrp) {
+                bool good = pair_has(u[q][0], tag) && pair_has(u[q][1], tag) &&
+                            pair_has(u[q][2], tag) && pair_has(u[q][3], tag);
+                if (!good && ok)
+                  good = ld_group_tagged(sums + (size_t)b * H + 4 * (size_t)g, tag, &s_abort, u[q]);
+                if (!good) ok = false;
+                a[q] = make_float4(pair_val(u[q][0]), pair_val(u[q][1]), pair_val(u[q][2]),
+                                   pair_val(u[q][3]));
+              }
             }
           }
 #pragma unroll
@@ -889,10 +896,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
       }
       if (c == 0 && tid == 0) {
-        if (K) {
-          xflag[XCH_BASE] = xbase + (unsigned)L * (unsigned)G;
-          xflag[XCH_LAYERS] = xl0 + (unsigned)L;
-        }
+        if (K) xflag[XCH_LAYERS] = xl0 + (unsigned)L;
         ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)L * (unsigned)G);
         ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
         ws.hdr[HDR_NSEG] = -1;  // this kernel's segment lists are per half: not resumable

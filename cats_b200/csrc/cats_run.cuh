@@ -14,6 +14,7 @@ namespace cats {
 struct DevInfo {
   int sms = 0;
   int max_smem_optin = 0;
+  int clock_khz = 0;  // SM clock (cycles per millisecond): converts the wait limit to cycles
 };
 const DevInfo& dev_info();  // per-device properties of the current device (cats_abi.cu)
 extern int g_use_pdl;       // cats_set_option("pdl", 0) launches without programmatic dependencies
@@ -63,6 +64,7 @@ inline int updown_ctas(int I) {
 struct TmaPlan {
   bool ok = false, xs = false;
   int S = 0, grid = 0, sr = 1, nvt = 1, cap = 0, rmax = 0, cw = 1, pw = 1;
+  int wait_kc = 0;  // limit of every wait in the kernel, in units of 1024 clock cycles
   size_t smem = 0;
 };
 
@@ -70,6 +72,7 @@ struct TmaPlan {
 struct MegaPlan {
   bool ok = false;
   int S = 0, cw = 1, grid = 0, nvt = 1, cap = 0, rmax = 0, bulk_flush = 0, mma_dot = 0, parts = kParts;
+  int wait_kc = 0;
   size_t smem = 0;
 };
 

@@ -28,7 +28,12 @@ constexpr int kTmaThreads = kConsumerThreads + 32 * kMaxProducerWarps;  // launc
 // stage is one 8 KB row; two issuing threads lift that.  pw must divide the stage count so that
 // each ring slot is always refilled by the same producer (it has then waited on every earlier
 // phase of that slot's barrier itself).
-constexpr long long kWaitCycles = 2000000000LL;     // ~1 s at B200 clocks
+// Every wait is bounded.  The limit lives in shared memory right behind the CTA's abort flag
+// (abort[1], in units of 1024 clock cycles; the host derives it from the "wait_ms" option and the
+// device's clock rate, default 1000 ms), so one pointer gives a wait both.
+__device__ __forceinline__ long long wait_limit(volatile int* abort) {
+  return (long long)abort[1] << 10;
+}
 
 enum { STATUS_OK = 0, STATUS_WAIT_TIMEOUT_GATE = 1, STATUS_WAIT_TIMEOUT_UPDOWN = 2 };
 
@@ -74,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort) return false;
     const long long dt = clock64() - t0;
     if (dt > 20000) __nanosleep(100);
-    if (dt > kWaitCycles) {
+    if (dt > wait_limit(abort)) {
       *abort = 1;
       return false;
     }
@@ -280,9 +285,10 @@ template <typename T, int BT, int SR, bool XS>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, int H, int I,
            float thr, T* __restrict__ gate_dense, uint8_t* __restrict__ flag_dense, int S,
-           int cw, int rmax) {
+           int cw, int rmax, int wait_kc) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_abort;
+  __shared__ int s_ctl[2];  // abort flag, wait limit
+  int& s_abort = s_ctl[0];
   const uint32_t row_bytes = (uint32_t)H * sizeof(T), stage_bytes = SR * row_bytes;
   unsigned char* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * stage_bytes);
@@ -311,6 +317,7 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
       mbar_init(empty_u + 8u * s, 1);
     }
     s_abort = 0;
+    s_ctl[1] = wait_kc;
     mbar_fence_init();
   }
   __syncthreads();
@@ -424,7 +431,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
 k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restrict__ WdT,
              WsPtrs ws, int B, int H, int I, int cap, T* __restrict__ out, int out_mode,
              T* __restrict__ resid, T* __restrict__ x_next, const T* __restrict__ norm_w,
-             float eps, int S, int cw) {
+             float eps, int S, int cw, int wait_kc) {
   using V = VecT<T>;
   constexpr int N = V::N;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -432,7 +439,8 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
   __shared__ int s_part[kWarps + 2];
   __shared__ float s_red[32];
   __shared__ int s_last;
-  __shared__ int s_abort;
+  __shared__ int s_ctl[2];  // abort flag, wait limit
+  int& s_abort = s_ctl[0];
 
   const uint32_t row_bytes = (uint32_t)H * sizeof(T);
   unsigned char* ring = smem;
@@ -453,6 +461,7 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
       mbar_init(empty_u + 8u * s, kConsumerWarps);
     }
     s_abort = 0;
+    s_ctl[1] = wait_kc;
     mbar_fence_init();
   }
   // x is the input of this layer's stage 1 as well: it was final before that grid started, so

@@ -12,6 +12,7 @@ PyTorch is used for device memory and streams only; all arithmetic happens in
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -381,20 +382,24 @@ def histogram_threshold(counts: torch.Tensor, edges: torch.Tensor, sparsity: flo
     return out
 
 
-# Packed WdT per down_proj weight.  Keyed on storage pointer, shape, dtype and the tensor's
-# in-place version counter, so a weight that is modified or replaced is re-packed.
+# Packed WdT per down_proj weight.  An entry belongs to one live tensor object: it is found again
+# only by that same object (a weak reference is compared, not the address - the caching allocator
+# hands the address of a freed weight to the next tensor of the same shape), it is re-packed when
+# the tensor was modified in place (version counter) and it is dropped, together with its
+# (I, H) copy on the GPU, when the weight tensor is garbage collected.
 _packed = {}
 
 
 def packed_wdt(wd: torch.Tensor) -> torch.Tensor:
     """WdT (I, H) for a down_proj weight given in nn.Linear layout (H, I); packed on first use."""
-    key = (wd.data_ptr(), tuple(wd.shape), wd.dtype, wd.device.index)
+    key = id(wd)
     hit = _packed.get(key)
-    if hit is not None and hit[0] == wd._version:
-        return hit[1]
+    if hit is not None and hit[0]() is wd and hit[1] == wd._version and hit[2] == wd.data_ptr():
+        return hit[3]
     _req(wd, "down weight (H, I)")
     wdt = transpose(wd)
-    _packed[key] = (wd._version, wdt)
+    ref = weakref.ref(wd, lambda _r, k=key: _packed.pop(k, None))
+    _packed[key] = (ref, wd._version, wd.data_ptr(), wdt)
     return wdt
 
 

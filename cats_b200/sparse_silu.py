@@ -6,7 +6,11 @@ constructor keywords, attributes (``is_profile``, ``sp_method``, ``dead_threshol
 ``kill_sparse_swish_outputs``, ``use_relu``, ``is_stats`` ...) and ``forward(x, sp_mask=None)``,
 and the model-level helpers the reference's bench scripts call (``apply_sparse_silu_mlp``,
 ``enable_sparse_silu``, ``activate_stats``, ``load_act_hist``, ``set_sparse_threshold``, ...;
-experiments/bench_sparse_inference_llama.py:38-77).
+experiments/bench_sparse_inference_llama.py:38-77), and the model-level classes those scripts
+build their models from: ``get_sparse_config`` (:95-116), ``SparseLlamaConfig`` /
+``SparseLlamaForCausalLM`` (:771-804), ``SparseMistralConfig`` / ``SparseMistralforCausalLM``
+(:732-768) - so ``from cats_b200.sparse_silu import *`` gives a bench script every name it
+takes from ``ugly_utils`` (``torch`` included, which the scripts use without importing it).
 
 Dispatch of ``forward`` when ``is_profile`` is set (as in the reference, :877-904):
   decode (x.shape[1] == 1), sp_method 1 or 2 -> the CUDA path (``ops.mlp``); the reference calls
@@ -24,8 +28,10 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
-
 from . import ops
+
+MISTRAL = "mistral"   # model_type strings of the reference's utils/constants.py
+LLAMA = "llama"
 
 
 class SparseSiLU(nn.SiLU):
@@ -238,11 +244,21 @@ def _layers(model):
     return model.model.layers
 
 
+def get_model_type(model) -> str:
+    """MISTRAL or LLAMA from the model's class name - the reference's rule
+    (utils/utils.py:11-22): "mistral" is looked for first, then "llama"."""
+    name = model.__class__.__name__.lower()
+    if MISTRAL in name:
+        return MISTRAL
+    if LLAMA in name:
+        return LLAMA
+    raise ValueError(f"Model name {name} is not recognized.")
+
+
 def get_mlp_class(model):
-    """Mistral models get MistralSparseSiluMLP, everything else the Llama class — the reference's
-    rule (ugly_utils.py:64-66, utils/utils.py:11-22), decided here from the config's model_type."""
-    mt = str(getattr(getattr(model, "config", None), "model_type", "")).lower()
-    return MistralSparseSiluMLP if "mistral" in mt else LlamaSparseSiluMLP
+    """Mistral models get MistralSparseSiluMLP, Llama models LlamaSparseSiluMLP
+    (ugly_utils.py:64-66)."""
+    return MistralSparseSiluMLP if get_model_type(model) == MISTRAL else LlamaSparseSiluMLP
 
 
 def apply_sparse_silu_mlp(model, config, use_sparse_regularization: bool = False):
@@ -338,3 +354,29 @@ def load_act_hist(model, filename: str):
     for i, mlp in _sparse_mlps(model):
         if mlp.is_stats:
             mlp.histogram_bins, mlp.pre_act_hist_counts, mlp.post_act_hist_counts = act_dict[i]
+
+
+
+# ---- model-level classes (cats_b200/sparse_models.py), imported on first use --------------------
+# They subclass the HF Llama / Mistral models, and importing those takes seconds, which the
+# operator-level users of this module should not pay.  ``__all__`` lists them, so
+# ``from cats_b200.sparse_silu import *`` still delivers every name (that is what triggers the
+# import then).
+_MODEL_NAMES = ("get_sparse_config", "SparseLlamaConfig", "SparseLlamaForCausalLM",
+                "SparseMistralConfig", "SparseMistralforCausalLM")
+
+__all__ = [
+    "torch", "nn", "os", "MISTRAL", "LLAMA", "SparseSiLU", "CatsSparseSiluMLP",
+    "LlamaSparseSiluMLP", "MistralSparseSiluMLP", "get_model_type", "get_mlp_class", "apply_sparse_silu_mlp",
+    "activate_stats", "deactivate_stats", "enable_sparse_silu", "disable_sparse_silu",
+    "print_dead_neuron_stats", "get_threshold", "set_sparse_threshold", "save_act_hist",
+    "load_act_hist", *_MODEL_NAMES,
+]
+
+
+def __getattr__(name):
+    if name in _MODEL_NAMES:
+        from . import sparse_models
+
+        return getattr(sparse_models, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -3,8 +3,9 @@
 This is the decode loop of the MLP halves of a decoder: for every layer, the CATS MLP of the
 RMS-normalised residual is added back to the residual (the reference's decoder layer does
 norm -> mlp -> residual add, experiments/models/sparse_silu/ugly_utils.py:1036-1057).  The
-residual add and the next layer's RMS norm are fused into the last CTA of each layer's down
-projection, so a token costs two kernel launches per layer and nothing else.
+residual add and the next layer's RMS norm are fused into the kernel: where the shape allows,
+the whole stack is ONE launch of the persistent cooperative kernel per token
+(``launches_per_step``), else a stage-1 and a stage-2/3 launch per layer.
 
 ``CatsMLPStack.decode_step`` is the host-buffer entry point: it copies the token's hidden state
 from pinned host memory, runs all layers and copies the result back.
@@ -51,7 +52,8 @@ class CatsMLPStack:
         self.out_host = torch.zeros((batch, self.H), dtype=self.dtype).pin_memory()
         self.h2d_bytes = self.x_host.numel() * self.x_host.element_size()
         self.d2h_bytes = self.out_host.numel() * self.out_host.element_size()
-        self.launches_per_step = 2 * self.L
+        persistent = _lib.lib().cats_uses_persistent_kernel(self.L, batch, self.H, self.I, self.code)
+        self.launches_per_step = 1 if persistent == 1 else 2 * self.L
 
     def run_device(self) -> None:
         """All layers on the state already in ``self.x`` / ``self.resid`` (device resident)."""

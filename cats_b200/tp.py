@@ -12,8 +12,8 @@ run because nothing crosses ranks before the sum.
 
 ``FusedTPStack`` is the product path: ONE persistent kernel per GPU and token
 (``cats_tp_mlp_stack``) whose CTAs push their slice of the layer's partial sums into every peer's
-exchange buffer over NVLink and add the ranks' partials themselves — no collective library call,
-no kernel boundary between layers.  ``TPStack`` (kernels + one NCCL all-reduce per layer in a CUDA
+exchange buffer over NVLink, add the ranks' partials of that slice themselves and hand the total
+to the other CTAs of their GPU — no collective library call, no kernel boundary between layers.  ``TPStack`` (kernels + one NCCL all-reduce per layer in a CUDA
 graph) is kept as the baseline it is measured against.
 
 ``shard_rows`` / ``shard_layer`` are pure tensor slicing and run anywhere; ``TPStack`` drives the
@@ -200,6 +200,7 @@ class FusedTPStack:
         self._thr = (ctypes.c_float * self.L)(*[float(l.threshold) for l in self.layers])
         self._dt = ops.dtype_code(self.dtype)
         self.launches_per_step = 1
+        self.failed = False
 
     def set_input(self, x: torch.Tensor) -> None:
         self.x.copy_(x.reshape(self.B, self.H), non_blocking=True)
@@ -211,6 +212,11 @@ class FusedTPStack:
     def run_device(self) -> None:
         from . import _lib
 
+        if self.failed:
+            raise RuntimeError(
+                "cats_b200.tp: a wait inside the tensor-parallel kernel ran out earlier; the "
+                "workspace and every rank's exchange buffer are invalid - build a new "
+                "FusedTPStack on all ranks")
         with torch.cuda.device(self.device):
             st = _lib.lib().cats_tp_mlp_stack(
                 self.L, self._wg, self._wu, self._wd, self._thr, self.x.data_ptr(),
@@ -220,7 +226,20 @@ class FusedTPStack:
         _lib.check(st, "cats_tp_mlp_stack")
 
     def device_status(self) -> int:
-        return self.ws.counters()[1]
+        """Sticky device status word (synchronises the stream).  Non-zero: a bounded wait ran
+        out (a peer never arrived); this stack refuses further launches."""
+        status = self.ws.counters()[1]
+        if status != 0:
+            self.failed = True
+        return status
+
+    def check(self) -> None:
+        """Raise if a wait inside the kernel ran out (synchronises the stream)."""
+        status = self.device_status()
+        if status != 0:
+            raise RuntimeError(f"cats_b200.tp: device status {status}: a bounded wait ran out "
+                               "inside cats_tp_mlp_stack (peer missing or late); all ranks must "
+                               "re-create their exchange buffers and workspaces")
 
     def close(self) -> None:
         self.xb.close()

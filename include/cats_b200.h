@@ -72,9 +72,14 @@ int cats_sm_count(void);
  * shape allows (default 1; 0 = one stage-1 and one stage-2/3 launch per layer).  Inside the
  * persistent kernel: "bulk_flush" (0/1, default 1: accumulators leave through TMA bulk reduces),
  * "mma_dot" (0/1, default 1: tensor-core dot products for batches of 2-4 with 16-bit weights),
- * "parts" (0 = automatic, or 1..3 parts per layer).  The same values are read once from the
- * environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL, CATS_B200_MEGA,
- * CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT and CATS_B200_PARTS.  No reference counterpart.
+ * "parts" (0 = automatic, or 1..3 parts per layer).  "wait_ms": limit of every wait inside a
+ * kernel (on a shared-memory barrier, a grid barrier, another rank's data), default 1000; a wait
+ * that runs out makes the kernel leave in an orderly way and sets the device status word (see
+ * cats_read_counters); waits for other ranks get four times the limit.  The same values are read
+ * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
+ * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS and CATS_B200_WAIT_MS.
+ * No reference counterpart (the reference has no device-side waits; its error path is exit(-1),
+ * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:25-33, 2397-2400).
  */
 int cats_set_option(const char* name, int value);
 
@@ -141,6 +146,9 @@ int cats_down(const void* WdT, void* ws, size_t ws_bytes, int B, int H, int I, i
  *   x_next [B, H] (dtype)  RMS-normalised new residual: resid / sqrt(mean(resid^2) + eps),
  *                          times norm_weight[H] (dtype) when that is not NULL
  * (resid/x_next require out_mode == CATS_OUT_STORE; `out` may be NULL when resid is given.)
+ * Ordering: x must be final before the launch that precedes this one in the stream has started
+ * (true when that launch is this layer's cats_gate or cats_compact, which read the same x): the
+ * kernel copies x into shared memory before it waits for its predecessor to finish.
  */
 int cats_updown(const void* x, const void* Wu, const void* WdT, void* ws, size_t ws_bytes,
                 int B, int H, int I, int dtype, void* out, int out_mode, void* resid,
@@ -181,6 +189,9 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
  *     on the GPU (different streams, no ordering between them) race on it: keep the calls of a
  *     device in one stream or order them with events.
  *   - out[B, H] has the element type dtype and is overwritten; arguments as for cats_mlp.
+ *   - A wait inside the kernels that ran out ("wait_ms") leaves a sticky status word in the
+ *     array; cats_mlp_static_status reads it (it blocks until `stream` is idle).  No call clears
+ *     it: after a non-zero status the process should stop using this entry point on that device.
  * This entry point has no counterpart in the reference (its ops allocate their scratch with
  * cudaMalloc on every call).
  */
@@ -189,6 +200,9 @@ int cats_mlp_static(const void* x, const void* Wg, const void* Wu, const void* W
 
 /* Size in bytes of the built-in scratch array of cats_mlp_static. */
 size_t cats_mlp_static_limit(void);
+
+/* Device status word of the built-in array on the current device (0 = no wait ever ran out). */
+int cats_mlp_static_status(int* device_status, void* stream);
 
 /*
  * A stack of L CATS MLP layers chained through the fused residual + RMS-norm tail, launched
@@ -209,18 +223,23 @@ int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const vo
  * the unsharded ones) and runs cats_tp_mlp_stack at the same time as its peers: the persistent
  * kernel of cats_mlp_stack, whose CTAs, at the end of every layer, store their slice of this
  * rank's partial sums straight into every peer's exchange buffer over NVLink (plain peer stores
- * of 8-byte value + layer-tag pairs, so no fence is needed on either side; no TMA involved),
- * wait until every rank's partials have arrived in their own buffer, and add them in rank
- * order, so that every rank computes bit-identical residuals and inputs for the next layer.  x_io / resid [B, H] as for
- * cats_mlp_stack, replicated on every rank.  B <= 4.
+ * of 8-byte value + layer-tag pairs, every pair one 64-bit element of its store and of its load,
+ * so no fence, flag or counter is needed on either side; no TMA involved), add the ranks'
+ * partial sums of that slice in rank order as they arrive in their own buffer - every rank
+ * computes bit-identical residuals and inputs for the next layer - and publish the total, tagged
+ * the same way, to the other CTAs of their GPU.  x_io / resid [B, H] as for cats_mlp_stack,
+ * replicated on every rank.  B <= 4.
  *
  * exchange[p] (host array of nranks device pointers) is rank p's exchange buffer as mapped into
  * the calling process; exchange[rank] is the caller's own.  Every rank creates its buffer with
  * cats_tp_exchange_alloc (cudaMalloc + clear + CUDA IPC handle, 64 bytes), passes the handle to
  * its peers by any host channel, and maps theirs with cats_tp_exchange_open.  All ranks must make
  * the same sequence of cats_tp_mlp_stack calls (same L, B, H) on a set of buffers.
- * A rank whose peers never arrive gives up after a few seconds (bounded wait): the call still
+ * A rank whose peers never arrive gives up after 4 x "wait_ms" (bounded wait): the call still
  * returns CATS_OK (it is asynchronous) and cats_read_counters reports a non-zero device status.
+ * After a non-zero device status the workspace AND every rank's exchange buffer are invalid (the
+ * ranks' layer tags no longer agree): all ranks free their buffers, allocate and exchange new
+ * ones and clear their workspaces before the next call.
  * CATS_ERR_MODE: the shape cannot run as one persistent kernel with one CTA per SM on this GPU
  * (then use one all-reduce per layer around cats_mlp instead).  nranks == 1 is allowed (the
  * exchange then runs against the caller's own buffer).

@@ -100,13 +100,25 @@ class _Layer(torch.nn.Module):
         self.mlp.down_proj = torch.nn.Linear(I, H, bias=False)
 
 
-class _Model(torch.nn.Module):
-    def __init__(self, model_type, H=64, I=96, L=2):
+class _ModelBase(torch.nn.Module):
+    def __init__(self, H=64, I=96, L=2):
         super().__init__()
-        self.config = type("Cfg", (), {"model_type": model_type, "hidden_size": H,
-                                        "intermediate_size": I})()
+        self.config = type("Cfg", (), {"hidden_size": H, "intermediate_size": I})()
         self.model = torch.nn.Module()
         self.model.layers = torch.nn.ModuleList([_Layer(H, I) for _ in range(L)])
+
+
+# the model family is read off the class name, as in the reference (utils/utils.py:11-22)
+class TinyMistralForCausalLM(_ModelBase):
+    pass
+
+
+class TinyLlamaForCausalLM(_ModelBase):
+    pass
+
+
+def _Model(family, **kw):
+    return (TinyMistralForCausalLM if family == "mistral" else TinyLlamaForCausalLM)(**kw)
 
 
 def test_model_helpers_follow_the_bench_script_sequence(tmp_path):
