@@ -25,6 +25,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -44,10 +45,11 @@ WORKLOADS = {
     "llama7b_fp32": ("llama7b", torch.float32, 32, 0.5),
     "llama70b": ("llama70b", torch.bfloat16, 80, 0.7),
 }
-# dram__bytes_read + dram__bytes_write per layer of k_cats_mega for the default workload, from the
-# ncu capture summarised in profiles/k_cats_mega_mistral7b_fp16_s50_ncu_full.md (2 layers captured;
-# traffic is proportional to the number of layers)
-NCU_TRAFFIC_PER_LAYER = {("mistral7b", 0.5, 1): 236.7e6}
+# (dram__bytes_read + dram__bytes_write) / algorithmic bytes of k_cats_mega for the default
+# workload, from the ncu capture summarised in profiles/k_cats_mega_mistral7b_fp16_s50_ncu_full.md
+# (2 layers captured: 236.7 MB per layer against 234.8 MB algorithmic; DRAM traffic is the rows a
+# rank streams, so it grows with the layers and with the rows per rank like the algorithmic bytes)
+NCU_TRAFFIC_RATIO = {("mistral7b", 0.5, 1): 236.7e6 / 234.8e6}
 METRIC = "cats_mlp_stack_decode_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -69,6 +71,13 @@ def parse_args():
     ap.add_argument("--no-dense", action="store_true")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
                     help="N > 1: exchange inside the persistent kernel, or one NCCL all-reduce per layer")
+    ap.add_argument("--regions", type=int, default=10,
+                    help="timed regions of --steps steps each (the median is reported)")
+    ap.add_argument("--config5-layers", type=int, default=80)
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-config5", action="store_true")
+    ap.add_argument("--no-decoder", action="store_true")
     return ap.parse_args()
 
 
@@ -256,197 +265,533 @@ def event_time_ms(fn, iters, stream):
     return s.elapsed_time(e) / iters
 
 
-def per_launch_us(launch_one, n_items, repeats, stream):
-    """Mean duration of single launches, each bracketed by its own pair of CUDA events."""
+def per_launch_us(launch_one, n_items, repeats, stream, before=None):
+    """Durations of single launches, each bracketed by its own pair of CUDA events (``before``
+    runs ahead of each start event, e.g. an L2 flush).  Returns (mean, median, min, geomean)."""
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(n_items * repeats)]
     k = 0
     for _ in range(repeats):
         for i in range(n_items):
+            if before is not None:
+                before()
             evs[k][0].record(stream)
             launch_one(i)
             evs[k][1].record(stream)
             k += 1
     torch.cuda.synchronize()
     ts = [a.elapsed_time(b) * 1e3 for a, b in evs]
-    return statistics.mean(ts), statistics.median(ts), min(ts)
+    return (statistics.mean(ts), statistics.median(ts), min(ts),
+            math.exp(statistics.mean(math.log(max(t, 1e-3)) for t in ts)))
+
+
+class Dist:
+    """The process group of this run (or none), with the two operations the bench needs."""
+
+    def __init__(self):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dev = torch.device("cuda", self.local_rank)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        import torch.distributed as dist
+        t = torch.tensor([v], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def timed_regions(run, steps, regions, D: Dist, stream):
+    """``regions`` timed regions of exactly ``steps`` steps each: barrier + synchronize on both
+    sides, CUDA events on the launching stream, the maximum over ranks per region.  Returns the
+    per-step times in ms, one per region."""
+    out = []
+    for _ in range(regions):
+        D.barrier()
+        ms = event_time_ms(run, steps, stream)
+        D.barrier()
+        out.append(D.max_over_ranks(ms))
+    return out
+
+
+def spread(samples):
+    return {"median": statistics.median(samples), "min": min(samples), "max": max(samples),
+            "n": len(samples)}
+
+
+def hbm_peak():
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_layers(H, I, dtype, L, s, seed, D: Dist, keep_full=0):
+    """L layers on the device, sharded over the intermediate dimension when there are several
+    ranks (every rank generates the full layer from the seed and keeps its rows).  The first
+    ``keep_full`` unsharded layers are returned as well (for the parity check)."""
+    from cats_b200 import synth, tp
+
+    layers, full = [], []
+    for l in range(L):
+        layer = synth.make_layer(H, I, dtype, D.dev, seed * 1000 + l, s)
+        if l < keep_full:
+            full.append(layer)
+        layers.append(tp.shard_layer(layer, D.rank, D.world) if D.world > 1 else layer)
+    torch.cuda.synchronize()
+    return layers, full
+
+
+def layer_bytes(layers, n_act, B, H, esize):
+    I_local = layers[0].wg.shape[0]
+    return esize * I_local * H + 2 * esize * n_act * H + 4 * esize * B * H
+
+
+def active_counts(layers, x0, B, H, ws, limit=8):
+    """Active neurons (union over the batch) of the first layers for the input x0: stage 1 alone
+    plus the counter read-back.  For reporting, outside every timed region."""
+    from cats_b200 import ops
+
+    xin = x0.reshape(B, 1, H).contiguous()
+    counts = []
+    for l in layers[:limit]:
+        ops.gate(xin, l.wg, l.threshold, ws=ws)
+        counts.append(ws.counters()[0])
+    return counts
+
+
+def parity_block(full, x0, B, H, dtype, D: Dist, tol):
+    """The first layers through the product path against the CPU oracle of the UNSHARDED stack
+    (the checker; rank 0 computes it), and, with several ranks, bit-identity of the result across
+    ranks.  Raises outside the tolerance."""
+    import numpy as np
+
+    from cats_b200 import tp
+    from cats_b200.stack import CatsMLPStack
+    from oracle import cats_oracle as O
+
+    sub = [tp.shard_layer(l, D.rank, D.world) for l in full] if D.world > 1 else full
+    stack = tp.FusedTPStack(sub, batch=B) if D.world > 1 else CatsMLPStack(sub, batch=B)
+    for _ in range(2):                        # twice: the exchange slots alternate across launches
+        stack.set_input(x0)
+        stack.run_device()
+    torch.cuda.synchronize()
+    status = stack.ws.counters()[1]
+    same = True
+    if D.world > 1:
+        import torch.distributed as dist
+        for t in (stack.x, stack.resid):
+            parts = [torch.empty_like(t) for _ in range(D.world)]
+            dist.all_gather(parts, t)
+            same = same and all(torch.equal(parts[0], p) for p in parts)
+    block = None
+    if D.rank == 0:
+        f = lambda t: t.detach().float().cpu().numpy()
+        bf16 = lambda a: torch.from_numpy(np.asarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+        rnd = {torch.float16: np.float16, torch.float32: None, torch.bfloat16: bf16}[dtype]
+        xe, re_, _ = O.mlp_stack(f(x0), [(f(l.wg), f(l.wu), f(l.wdt).T) for l in full],
+                                 [l.threshold for l in full], round_to=rnd)
+        block = {"layers": len(full), "rel_l2_x": O.rel_l2(f(stack.x), xe),
+                 "rel_l2_resid": O.rel_l2(f(stack.resid), re_), "tolerance": tol,
+                 "identical_across_ranks": bool(same), "device_status": int(status),
+                 "against": "CPU oracle of the unsharded stack (oracle/cats_oracle.py:mlp_stack)"}
+    if D.world > 1:
+        stack.close()
+    ok = torch.tensor([1], device=D.dev)
+    if D.rank == 0 and not (block["rel_l2_x"] <= tol and block["rel_l2_resid"] <= tol and same
+                            and status == 0):
+        ok.zero_()
+    if D.world > 1:
+        import torch.distributed as dist
+        dist.broadcast(ok, 0)
+    if int(ok.item()) == 0:
+        if D.rank == 0:
+            sys.stderr.write("PARITY FAILURE: " + json.dumps(block) + "\n")
+        raise SystemExit(3)
+    return block
+
+
+def build_tp_stack(layers, B, x0, mode, D: Dist):
+    """Several ranks: the fused stack (one persistent kernel per GPU, exchange inside), or the
+    kernels + one NCCL all-reduce per layer in a CUDA graph."""
+    import torch.distributed as dist
+
+    from cats_b200 import tp
+
+    stack, why = None, ""
+    if mode == "fused":
+        try:
+            stack = tp.FusedTPStack(layers, batch=B)
+            stack.set_input(x0)
+            stack.run_device()
+            torch.cuda.synchronize()
+            stack.check()
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line
+            why, stack = f"{type(e).__name__}: {e}"[:200], None
+        okf = torch.tensor([1 if stack is not None else 0], device=D.dev)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        if int(okf.item()) == 0:
+            stack = None
+    if stack is not None:
+        return stack, "fused"
+    stack = tp.TPStack(layers, batch=B)
+    stack.set_input(x0)
+    stack.capture()
+    return stack, ("nccl" if mode == "nccl" else f"nccl (fused unavailable: {why or 'on another rank'})")
+
+
+def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=True, parity_layers=0,
+                  sample_clocks=False):
+    """Build a stack of the given shape (sharded when there are several ranks), time it and
+    return a result block: us/layer, tokens/s, achieved GB/s per rank against the HBM peak."""
+    from cats_b200 import _lib, ops, synth, tp
+    from cats_b200.stack import CatsMLPStack
+
+    esize = torch.empty((), dtype=dtype).element_size()
+    stream = torch.cuda.current_stream(D.dev)
+    layers, full = make_layers(H, I, dtype, L, s, args.seed, D, keep_full=parity_layers)
+    x0 = synth.make_x(B, H, dtype, D.dev, args.seed + 5).reshape(B, H)
+    parity = None
+    if parity_layers:
+        tol = {torch.float32: 1e-3, torch.float16: 2e-2, torch.bfloat16: 5e-2}[dtype]
+        parity = parity_block(full, x0, B, H, dtype, D, tol)
+        del full
+    if D.world == 1:
+        stack, mode = CatsMLPStack(layers, batch=B), "single GPU"
+        persistent = stack.launches_per_step == 1
+    else:
+        stack, mode = build_tp_stack(layers, B, x0, args.tp, D)
+        persistent = isinstance(stack, tp.FusedTPStack)
+    stack.set_input(x0)
+    for _ in range(max(3, args.warmup)):
+        stack.run_device()
+    clocks = None
+    if sample_clocks:      # SM clock and throttle reasons DURING the timed regions
+        with ClockSampler(D.local_rank) as sampler:
+            samples = timed_regions(stack.run_device, args.steps, regions, D, stream)
+        clocks = sampler.summary()
+    else:
+        samples = timed_regions(stack.run_device, args.steps, regions, D, stream)
+    ms = statistics.median(samples)
+    if persistent and D.world > 1:
+        stack.check()
+    n_act = statistics.mean(active_counts(layers, x0, B, H, stack.ws))
+    by = layer_bytes(layers, n_act, B, H, esize)
+    peak, peak_src = hbm_peak()
+    us_layer = ms * 1e3 / L
+    block = {
+        "workload": f"{name}: {L} layers, hidden {H}, intermediate {I}, "
+                    f"{str(dtype).replace('torch.', '')}, sparsity {s}, batch {B}",
+        "mode": mode, "layers": L, "us_per_layer": us_layer, "tokens_per_s": B * 1e3 / ms,
+        "ms_per_step": ms, "ms_per_step_samples": samples, "bytes_per_layer_per_rank": by,
+        "GBps_per_rank": by / us_layer / 1e3, "frac_of_peak": by / us_layer / 1e3 / peak,
+        "frac_of_8TBps": by / us_layer / 1e3 / 8000.0, "peak_source": peak_src,
+        "n_active_mean_per_rank": n_act, "intermediate_local": layers[0].wg.shape[0],
+        "kernel": "k_cats_mega" if persistent else "staged kernels",
+    }
+    if parity is not None:
+        block["parity"] = parity
+    if clocks is not None:
+        block["clocks"] = clocks
+    if D.world > 1 and persistent and with_nccl:
+        ref = tp.TPStack(layers, batch=B)
+        ref.set_input(x0)
+        ref.capture()
+        for _ in range(3):
+            ref.run_device()
+        rs = timed_regions(ref.run_device, max(5, args.steps // 2), 3, D, stream)
+        block["nccl_allreduce_variant"] = {
+            "us_per_layer": statistics.median(rs) * 1e3 / L,
+            "what": "stage kernels + one NCCL all-reduce + tail per layer, CUDA graph",
+            "speedup_of_fused": statistics.median(rs) / ms}
+    return block, stack, layers, x0
+
+
+def single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act, esize, peak):
+    """What a decoder sees: ONE ``cats_mlp`` call per layer.  (a) back to back over the distinct
+    layers' weights (nothing stays in L2), one event pair per call; (b) the reference's
+    micro-benchmark protocol, flash_gemv/bench/utils.py:12-58: an L2 flush (zero_() of a 512 MB
+    buffer) before every timed call, per-call events, geometric mean - plus the reference's
+    "Optimal" column (flash_gemv/bench/profile_llama7B.py:66-69): the dense MLP with the
+    intermediate dimension cut down to the active count."""
+    import torch.nn.functional as F
+
+    from cats_b200 import ops
+
+    L = len(layers)
+    xin = x0.reshape(B, 1, H).contiguous()
+    out = torch.empty_like(xin)
+    call = lambda i: ops.mlp(xin, layers[i].wg, layers[i].wu, layers[i].wdt, layers[i].threshold,
+                             out=out, ws=ws)
+    for i in range(min(L, 4)):
+        call(i)
+    reps = max(1, 128 // L)
+    b2b = per_launch_us(call, L, reps, stream)
+    by = esize * I * H + 2 * esize * n_act * H + 4 * esize * B * H
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=xin.device)
+    fl = per_launch_us(call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
+    k = int(round(n_act))
+    dense_call = lambda i: F.linear(F.silu(F.linear(xin, layers[i].wg)) * F.linear(xin, layers[i].wu),
+                                    layers[i].wdt.t())
+    opt_call = lambda i: F.linear(F.silu(F.linear(xin, layers[i].wg[:k])) * F.linear(xin, layers[i].wu[:k]),
+                                  layers[i].wdt[:k].t())
+    for i in range(2):
+        dense_call(i), opt_call(i)
+    dn = per_launch_us(dense_call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
+    op = per_launch_us(opt_call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
+    del flush
+    row = lambda t: {"mean_us": t[0], "median_us": t[1], "min_us": t[2], "geomean_us": t[3]}
+    return {
+        "what": "one cats_mlp call per layer (single-layer launch of the persistent kernel)",
+        "back_to_back": dict(row(b2b), GBps=by / b2b[1] / 1e3, frac_of_peak=by / b2b[1] / 1e3 / peak),
+        "reference_protocol": {
+            "protocol": "L2 flush (512 MB zero_) before every call, per-call CUDA events, geometric "
+                        "mean (flash_gemv/bench/utils.py:12-58)",
+            "k_active": k, "cats": row(fl), "dense_cublas": row(dn),
+            "optimal_dense_with_I_equal_k": row(op),
+            "speedup_cats_over_dense_geomean": dn[3] / fl[3]},
+    }
+
+
+def sweep_block(args, D: Dist):
+    """Other configurations on one GPU, a few layers each: the sparsity sweep of the Mistral
+    shape, the Llama-2-7B shape in fp16 and fp32 (fp32 = the single-layer CPU configuration),
+    and batches."""
+    out = []
+    cases = [("mistral7b", torch.float16, s, 1, 8) for s in (0.3, 0.7, 0.9)]
+    cases += [("llama7b", torch.float16, 0.5, 1, 8), ("llama7b", torch.float32, 0.5, 1, 6)]
+    cases += [("mistral7b", torch.float16, 0.5, b, 6) for b in (2, 4, 8, 16)]
+    from cats_b200 import synth
+    import torch.nn.functional as F
+
+    for shape, dtype, s, B, L in cases:
+        H, I = synth.SHAPES[shape]
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = max(10, args.steps // 2), 3
+        block, stack, layers, x0 = measure_stack(shape, H, I, dtype, L, s, B, sub, D, regions=3,
+                                                 with_nccl=False)
+        if B > 1:   # the dense cuBLAS MLP at the same batch, same chaining, CUDA graph
+            block["dense_cublas_us_per_layer"] = dense_stack_us(layers, x0, B, H, dtype, sub, D)
+            block["speedup_of_cats"] = block["dense_cublas_us_per_layer"] / block["us_per_layer"]
+        del block["ms_per_step_samples"]
+        out.append(block)
+        del stack, layers
+        torch.cuda.empty_cache()
+    return out
+
+
+def dense_stack_us(layers, x0, B, H, dtype, args, D: Dist):
+    """us/layer of the dense SiLU-gated MLP stack on cuBLAS (torch F.linear x3 + SiLU*mul +
+    residual/RMS-norm per layer), replayed from a CUDA graph."""
+    import torch.nn.functional as F
+
+    stream = torch.cuda.current_stream(D.dev)
+    xs = x0.reshape(B, 1, H).clone()
+    L = len(layers)
+
+    def dense_step():
+        xx, r = xs, xs
+        for l in layers:
+            y = F.linear(F.silu(F.linear(xx, l.wg)) * F.linear(xx, l.wu), l.wdt.t())
+            r = r + y
+            xx = (r.float() * torch.rsqrt(r.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(dtype)
+        return xx
+
+    g = torch.cuda.CUDAGraph()
+    sside = torch.cuda.Stream(D.dev)
+    sside.wait_stream(stream)
+    with torch.cuda.stream(sside):
+        for _ in range(2):
+            dense_step()
+    stream.wait_stream(sside)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        dense_step()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    ms = statistics.median(event_time_ms(g.replay, max(5, args.steps // 4), stream) for _ in range(3))
+    del g
+    return ms * 1e3 / L
+
+
+def decoder_block(family, prompt_len, gen, batches, args, D: Dist, eager=True):
+    """Configs 3 / 4: the full decoder (random init, fp16, 32 layers), greedy decode after a
+    uniform-random prompt, tokens 2..N timed with CUDA events on the device; CATS MLPs against the
+    same decoder with dense MLPs, both replayed from CUDA graphs (and eager at batch 1)."""
+    from cats_b200 import decoder as DEC
+
+    t_build = time.perf_counter()
+    model = DEC.build_random_model(family, torch.float16, D.dev, seed=args.seed)
+    thr = DEC.calibrate(model, 0.5, n_prompts=4, prompt_len=128, seed=args.seed + 1)
+    build_s = time.perf_counter() - t_build
+    cfg = model.config
+    g = torch.Generator(device="cpu")
+    g.manual_seed(args.seed + 2)
+    out = {"workload": f"{family} decoder, random init N(0, 0.02^2), fp16: {cfg.num_hidden_layers} "
+                       f"layers, hidden {cfg.hidden_size}, intermediate {cfg.intermediate_size}, "
+                       f"{cfg.num_attention_heads} query / {cfg.num_key_value_heads} KV heads, vocab "
+                       f"{cfg.vocab_size}; prompt {prompt_len} uniform-random ids, {gen} greedy tokens; "
+                       "CATS at 50 % per-layer thresholds from seeded calibration prompts "
+                       "(activate_stats -> device histograms -> set_sparse_threshold)",
+           "thresholds_min_max": [min(thr), max(thr)], "build_and_calibrate_s": build_s,
+           "timing": "tokens 2..N, CUDA events on the device (time_util_nofile.py:2902-2994)",
+           "batches": {}}
+    for B in batches:
+        ids = torch.randint(0, cfg.vocab_size, (B, prompt_len), generator=g).to(D.dev)
+        res = {}
+        for mode in ("cats", "dense"):
+            dec = DEC.CatsDecoder(model, B, prompt_len + gen + 8, mlp=mode, thresholds=thr)
+            dec.prefill(ids)
+            _, tps, _ = dec.decode(gen, use_graph=True)
+            res[mode] = {"tokens_per_s_graph": tps, "ms_per_token_graph": B * 1e3 / tps}
+            if eager and B == 1:
+                dec.prefill(ids)
+                _, tps_e, _ = dec.decode(min(gen, 128), use_graph=False)
+                res[mode]["tokens_per_s_eager"] = tps_e
+            if mode == "cats":
+                torch.cuda.synchronize()
+                res[mode]["device_status"] = dec.ws.counters()[1]
+                res[mode]["mlp_launches_per_token"] = dec.mlp_launches_per_step
+            del dec
+            torch.cuda.empty_cache()
+        res["speedup_of_cats_graph"] = res["cats"]["tokens_per_s_graph"] / res["dense"]["tokens_per_s_graph"]
+        out["batches"][str(B)] = res
+    # the MLP's share of a decode step: the same 32 CATS MLPs alone (cats_mlp per layer, graph)
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def module_overhead_block(H, I, dtype, D: Dist):
+    """Host cost of ``CatsSparseSiluMLP.forward`` per decode call (what HF ``generate`` pays 32
+    times per token): wall time per call of a long unsynchronised loop against the kernel's
+    device time per call in the same loop."""
+    from cats_b200 import sparse_silu as S
+
+    m = S.LlamaSparseSiluMLP({"hidden_size": H, "intermediate_size": I}).to(D.dev, dtype)
+    with torch.no_grad():
+        for lin in (m.gate_proj, m.up_proj, m.down_proj):
+            lin.weight.normal_(0, 0.02)
+    m.is_profile, m.sp_method, m.dead_threshold = True, 1, torch.tensor(0.26)
+    x = torch.randn(1, 1, H, device=D.dev).to(dtype)
+    stream = torch.cuda.current_stream(D.dev)
+    with torch.no_grad():
+        for _ in range(20):
+            m(x)
+        torch.cuda.synchronize()
+        n = 300
+        # host cost: calls issued while the GPU is still busy with earlier ones never wait for it
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            m(x)
+        host_us = (time.perf_counter() - t0) / n * 1e6
+        e1.record(stream)
+        e1.synchronize()
+        dev_us = e0.elapsed_time(e1) * 1e3 / n
+    del m
+    return {"host_us_per_call": host_us, "device_us_per_call": dev_us,
+            "what": "CatsSparseSiluMLP.forward, decode, one layer's weights (L2-resident: the "
+                    "device time here is not a bandwidth figure), 300 calls without synchronising"}
 
 
 def run_gpu_arm(args):
     import torch.distributed as dist
 
-    from cats_b200 import _lib, ops, synth, tp
-    from cats_b200.stack import CatsMLPStack
+    from cats_b200 import _lib, ops, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    D = Dist()
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py --impl cats needs a CUDA device (no CPU fallback)")
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    torch.cuda.set_device(D.dev)
+    if D.world > 1:
+        dist.init_process_group("nccl", device_id=D.dev)
     H, I, dtype, L, s = workload_config(args)
     B = args.batch
     esize = torch.empty((), dtype=dtype).element_size()
+    stream = torch.cuda.current_stream(D.dev)
+    peak, peak_src = hbm_peak()
 
-    # ---- data: full layers are generated one at a time and sharded at once (TP) -------------
-    layers = []
-    for l in range(L):
-        layer = synth.make_layer(H, I, dtype, dev, args.seed * 1000 + l, s)
-        if world > 1:
-            layer = tp.shard_layer(layer, rank, world)
-        layers.append(layer)
-    torch.cuda.synchronize()
-    I_local = layers[0].wg.shape[0]
-    x0 = synth.make_x(B, H, dtype, dev, args.seed + 5).reshape(B, H)
-    stream = torch.cuda.current_stream(dev)
-
-    if world == 1:
-        stack = CatsMLPStack(layers, batch=B)
-        stack.x_host.copy_(x0.cpu())
-        run = stack.run_device
-    else:
-        # product path: one persistent kernel per GPU exchanging partial sums over NVLink itself;
-        # the kernels + NCCL all-reduce graph only if that cannot be set up on every rank
-        tp_mode, why = "fused", ""
-        stack = None
-        if args.tp == "fused":
-            try:
-                stack = tp.FusedTPStack(layers, batch=B)
-                stack.set_input(x0)
-                stack.run_device()
-                torch.cuda.synchronize()
-                if stack.device_status() != 0:
-                    raise RuntimeError("device status %d" % stack.device_status())
-            except Exception as e:  # noqa: BLE001 - reported in the JSON line
-                why, stack = f"{type(e).__name__}: {e}"[:200], None
-            okf = torch.tensor([1 if stack is not None else 0], device=dev)
-            dist.all_reduce(okf, op=dist.ReduceOp.MIN)
-            if int(okf.item()) == 0:
-                stack = None
-        if stack is None:
-            tp_mode = "nccl" if args.tp == "nccl" else f"nccl (fused unavailable: {why or 'on another rank'})"
-            stack = tp.TPStack(layers, batch=B)
-            stack.set_input(x0)
-            stack.capture()
-        run = stack.run_device
-        x_host = x0.cpu().pin_memory()
-        out_host = torch.empty_like(x_host).pin_memory()
-    stack.set_input(x0)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing ---------------------------------------------------------------
-    for _ in range(max(3, args.warmup)):
-        run()
-    barrier()
-    with ClockSampler(local_rank) as clocks:
-        ms = event_time_ms(run, args.steps, stream)
-        barrier()
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item())
+    # ---- headline: device-resident timing of the stack ---------------------------------------
+    head, stack, layers, x0 = measure_stack(args.workload, H, I, dtype, L, s, B, args, D,
+                                            regions=args.regions, sample_clocks=True,
+                                            parity_layers=min(3, L) if not args.no_parity else 0)
+    ms_step, us_layer = head["ms_per_step"], head["us_per_layer"]
+    I_local = head["intermediate_local"]
+    persistent = head["kernel"] == "k_cats_mega"
 
     # ---- end to end through the host-buffer entry point ------------------------------------
-    if world == 1:
-        def e2e_step():
-            stack.decode_step()
+    if D.world == 1:
+        stack.x_host.copy_(x0.cpu())
+        e2e_step = stack.decode_step
         h2d, d2h = stack.h2d_bytes, stack.d2h_bytes
+        api = "CatsMLPStack.decode_step (pinned host in/out, cats_mlp_stack C call)"
     else:
+        x_host = x0.cpu().pin_memory()
+        out_host = torch.empty_like(x_host).pin_memory()
+
         def e2e_step():
             stack.set_input(x_host)
             stack.run_device()
             out_host.copy_(stack.x, non_blocking=True)
             stream.synchronize()
         h2d = d2h = x_host.numel() * x_host.element_size()
+        api = ("FusedTPStack (pinned host in/out, one cats_tp_mlp_stack C call per rank)"
+               if persistent else "TPStack (CUDA graph of kernels + NCCL all-reduce)")
     for _ in range(3):
         e2e_step()
-    barrier()
-    ms_e2e = event_time_ms(e2e_step, args.steps, stream)
-    barrier()
-    t = torch.tensor([ms_e2e], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_e2e = float(t.item())
+    e2e_samples = timed_regions(e2e_step, args.steps, max(3, args.regions // 2), D, stream)
+    ms_e2e = statistics.median(e2e_samples)
 
     # ---- roofline of the kernel that ran in the timed region ------------------------------------
-    # Algorithmic bytes of one layer: all of Wg, the active rows of Wu and WdT, x in, out.
+    n_act = head["n_active_mean_per_rank"]
+    bytes_layer = head["bytes_per_layer_per_rank"]
+    bytes_gate = esize * I_local * H + esize * B * H
+    bytes_updown = 2 * esize * n_act * H + 2 * esize * B * H
     ws = stack.ws
     xin = x0.reshape(B, 1, H).clone()
     out = torch.empty_like(xin)
-    if world == 1:
-        stack.set_input(x0)
-        counts = stack.active_counts()
-    else:
-        counts = []
-        for l in layers[: min(L, 8)]:
-            ops.gate(xin, l.wg, l.threshold, ws=ws)
-            counts.append(ws.counters()[0])
-    n_act = statistics.mean(counts)
-    bytes_gate = esize * I_local * H + esize * B * H
-    bytes_updown = 2 * esize * n_act * H + 2 * esize * B * H
-    bytes_layer = bytes_gate + bytes_updown
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-    else:
-        peak, peak_src = 6650.0, "fallback"
-    us_layer = ms_step * 1e3 / L
-    if world == 1:
-        mega = _lib.lib().cats_uses_persistent_kernel(L, B, H, I_local, ops.dtype_code(dtype)) == 1
-    else:
-        mega = isinstance(stack, tp.FusedTPStack)
-        if mega and stack.device_status() != 0:
-            raise RuntimeError("a bounded wait ran out inside the tensor-parallel kernel")
-    # tensor parallel: the all-reduce variant timed beside the fused kernel (context)
-    nccl_variant = None
-    if world > 1 and mega and not args.no_dense:
-        ref_stack = tp.TPStack(layers, batch=B)
-        ref_stack.set_input(x0)
-        ref_stack.capture()
-        for _ in range(3):
-            ref_stack.run_device()
-        barrier()
-        ms_ref = event_time_ms(ref_stack.run_device, max(5, args.steps // 4), stream)
-        barrier()
-        t = torch.tensor([ms_ref], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        nccl_variant = {"us_per_layer": float(t.item()) * 1e3 / L,
-                        "what": "stage kernels + one NCCL all-reduce + tail per layer, CUDA graph",
-                        "speedup_of_fused": float(t.item()) / ms_step}
-    # the two staged kernels on their own (single launches bracketed by events, rotating over the
-    # layers): what a caller of the stage-level entry points gets, and the pre-fusion baseline
-    reps = max(1, min(10, 320 // L))
-    gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
-                            L, reps, stream)
-    ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
-    updown_us = per_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
-                              L, reps, stream)
-    staged = {
-        "k_gate_tma": {"us": gate_us[0], "bytes": bytes_gate, "GBps": bytes_gate / gate_us[0] / 1e3},
-        "k_updown_tma": {"us": updown_us[0], "bytes": bytes_updown,
-                         "GBps": bytes_updown / updown_us[0] / 1e3},
-    }
-    if mega:
-        # one launch of the persistent kernel = one step = L layers
+    staged = None
+    if B <= 4:
+        reps = max(1, min(10, 320 // L))
+        gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
+                                L, reps, stream)
+        ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
+        updown_us = per_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
+                                  L, reps, stream)
+        staged = {
+            "k_gate_tma": {"us": gate_us[0], "bytes": bytes_gate, "GBps": bytes_gate / gate_us[0] / 1e3},
+            "k_updown_tma": {"us": updown_us[0], "bytes": bytes_updown,
+                             "GBps": bytes_updown / updown_us[0] / 1e3},
+        }
+    if persistent:
         kname, launch_us, launch_bytes = "k_cats_mega", ms_step * 1e3, bytes_layer * L
-    else:
+    elif staged:
         kname = max(staged, key=lambda k: staged[k]["us"])
         launch_us, launch_bytes = staged[kname]["us"], staged[kname]["bytes"]
+    else:
+        kname, launch_us, launch_bytes = "k_gate + k_updown (per layer)", us_layer, bytes_layer
     achieved = launch_bytes / launch_us / 1e3
+    traffic = None
+    if persistent and (args.workload, s, B) in NCU_TRAFFIC_RATIO:
+        # measured dram bytes / algorithmic bytes of the captured launch, applied to this launch's
+        # algorithmic bytes (both grow in proportion to the rows a rank streams)
+        traffic = NCU_TRAFFIC_RATIO[(args.workload, s, B)] * launch_bytes
     roofline = {
         "bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "peak_source": peak_src,
-        "traffic": (NCU_TRAFFIC_PER_LAYER[(args.workload, s, B)] * L
-                    if mega and (args.workload, s, B) in NCU_TRAFFIC_PER_LAYER else None),
+        "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
         "bytes_per_launch": launch_bytes, "launch_us": launch_us,
-        "units_per_launch": f"{L} layers" if mega else "1 layer stage",
+        "units_per_launch": f"{L} layers" if persistent else "1 layer stage",
         "frac_of_8TBps_nominal": achieved / 8000.0,
         "layer": {"bytes": bytes_layer, "us": us_layer, "GBps": bytes_layer / us_layer / 1e3,
                   "frac": bytes_layer / us_layer / 1e3 / peak,
@@ -454,98 +799,108 @@ def run_gpu_arm(args):
         "staged_kernels": staged, "n_active_mean": n_act, "intermediate_local": I_local,
     }
 
-    # ---- statistics kernel beside the path (threshold calibration): HBM-bound stream ----------
-    stats = None
-    if world == 1 and not args.no_dense:
+    extra = {}
+    if D.world == 1 and not args.no_dense:
+        # ---- one layer per launch: what a decoder sees, and the reference's protocol ------------
+        if B <= 4:
+            extra["single_layer"] = single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act,
+                                                       esize, peak)
+        # ---- statistics kernel beside the path (threshold calibration): HBM-bound stream --------
         nval = 160 * 1000 * 1000                       # 320 MB of fp16 activations: larger than L2
-        vals = torch.nn.functional.silu(torch.randn(nval // 8, device=dev) * 1.28).to(dtype).repeat(8)
+        vals = torch.nn.functional.silu(torch.randn(nval // 8, device=D.dev) * 1.28).to(dtype).repeat(8)
         edges = torch.cat([torch.tensor([-torch.inf]), torch.linspace(-1, 1, 998),
-                           torch.tensor([torch.inf])]).to(dev)
-        hcounts = torch.zeros(999, dtype=torch.int64, device=dev)
+                           torch.tensor([torch.inf])]).to(D.dev)
+        hcounts = torch.zeros(999, dtype=torch.int64, device=D.dev)
         for _ in range(2):
             ops.histogram(vals, edges, hcounts, take_abs=True)
         h_us = per_launch_us(lambda i: ops.histogram(vals, edges, hcounts, take_abs=True), 1, 5, stream)
         hb = vals.numel() * vals.element_size()
-        stats = {"k_histogram": {"us": h_us[1], "bytes": hb, "GBps": hb / h_us[1] / 1e3,
-                                 "frac": hb / h_us[1] / 1e3 / peak,
-                                 "bound": "instruction issue (about 20 instructions per value), not HBM",
-                                 "what": f"|post-activation| histogram of {vals.numel()} {dtype} values "
-                                         "(SiLU of N(0, 1.28^2)), the reference's 999 bins"}}
+        roofline["stats_kernels"] = {"k_histogram": {
+            "us": h_us[1], "bytes": hb, "GBps": hb / h_us[1] / 1e3, "frac": hb / h_us[1] / 1e3 / peak,
+            "bound": "instruction issue (about 20 instructions per value), not HBM",
+            "what": f"|post-activation| histogram of {vals.numel()} {dtype} values "
+                    "(SiLU of N(0, 1.28^2)), the reference's 999 bins"}}
         del vals
+        # ---- dense cuBLAS MLP of the same shape (context) --------------------------------------
+        d_us = dense_stack_us(layers, x0, B, H, dtype, args, D)
+        extra["dense_cublas"] = {
+            "us_per_layer": d_us, "tokens_per_s": 1e6 / (d_us * L),
+            "what": "torch F.linear x3 + SiLU*mul + residual/RMS-norm per layer, CUDA graph",
+            "speedup_of_cats": d_us / us_layer}
+        extra["module_call"] = module_overhead_block(H, I, dtype, D)
 
-    # ---- dense cuBLAS MLP of the same shape (context; single GPU only) -----------------------
-    dense = None
-    if world == 1 and not args.no_dense:
-        import torch.nn.functional as F
+    if D.world > 1 and persistent:
+        stack.close()
+    del stack, layers
+    torch.cuda.empty_cache()
 
-        xs = x0.reshape(B, 1, H).clone()
-        wds = [l.wdt.t() for l in layers]
-
-        def dense_step():
-            xx, r = xs, xs
-            for l, wd in zip(layers, wds):
-                y = F.linear(F.silu(F.linear(xx, l.wg)) * F.linear(xx, l.wu), l.wdt.t())
-                r = r + y
-                xx = (r.float() * torch.rsqrt(r.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(dtype)
-            return xx
-
-        g = torch.cuda.CUDAGraph()
-        sside = torch.cuda.Stream(dev)
-        sside.wait_stream(stream)
-        with torch.cuda.stream(sside):
-            for _ in range(2):
-                dense_step()
-        stream.wait_stream(sside)
-        torch.cuda.synchronize()
-        with torch.cuda.graph(g):
-            dense_step()
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        ms_dense = event_time_ms(g.replay, max(5, args.steps // 4), stream)
-        dense = {"us_per_layer": ms_dense * 1e3 / L, "tokens_per_s": 1e3 / ms_dense,
-                 "what": "torch F.linear x3 + SiLU*mul + residual/RMS-norm per layer, CUDA graph",
-                 "speedup_of_cats": ms_dense / ms_step}
+    # ---- the other configurations ---------------------------------------------------------------
+    if D.world == 1 and not args.no_sweep:
+        extra["sweep"] = sweep_block(args, D)
+    if not args.no_config5:
+        H5, I5 = synth.SHAPES["llama70b"]
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = max(5, min(args.steps, 20)), 3
+        c5, st5, l5, _ = measure_stack("llama70b", H5, I5, torch.bfloat16, args.config5_layers, 0.7, 1,
+                                       sub, D, regions=5,
+                                       parity_layers=2 if not args.no_parity else 0)
+        c5["note"] = ("config 5: the 70B-shaped stack, the same layer count at every number of "
+                      "GPUs, sharded over the intermediate dimension")
+        if D.world > 1 and c5["kernel"] == "k_cats_mega":
+            st5.close()
+        del st5, l5
+        torch.cuda.empty_cache()
+        extra["config5"] = c5
+    if D.world == 1 and not args.no_decoder:
+        extra["decoder"] = {
+            "config3": decoder_block("llama", 128, 512, [1], args, D),
+            "config4": decoder_block("mistral", 512, 1024, [1, 4, 8], args, D, eager=False),
+        }
 
     def leave():
         """Multi-rank exit: a last barrier, then leave without tearing NCCL down — destroying the
         process group while a captured CUDA graph still references its collectives can block."""
-        if world > 1:
+        if D.world > 1:
             torch.cuda.synchronize()
             dist.barrier()
             sys.stdout.flush()
             sys.stderr.flush()
             os._exit(0)
 
-    if rank != 0:
+    if D.rank != 0:
         leave()
         return
 
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if D.world == 1 and not args.no_cpu_baseline:
         res = time_cpu(H, I, L, s, B, args.seed, args.cpu_sample_layers, seconds=args.cpu_seconds)
         cpu = cpu_baseline_block(res, L, H, I, B)
 
+    launches = 1 if persistent else 2 * L
     line = {
-        "metric": METRIC, "value": 1e3 / ms_step, "unit": UNIT, "n_gpus": world,
+        "metric": METRIC, "value": B * 1e3 / ms_step, "unit": UNIT, "n_gpus": D.world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "ms_per_step_samples": head["ms_per_step_samples"],
+        "timed_regions": {"count": len(head["ms_per_step_samples"]), "steps_each": args.steps,
+                          "statistic": "median of the regions' per-step times (each the max over ranks)",
+                          **spread(head["ms_per_step_samples"])},
         "us_per_layer": us_layer, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": {torch.float16: "f16", torch.bfloat16: "bf16",
                                        torch.float32: "f32"}[dtype] + " storage, f32 accumulate",
-        "data": "synthetic", "config": config_block(args, H, I, dtype, L, s, world),
-        "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "api": "CatsMLPStack.decode_step (pinned host in/out, cats_mlp_stack C call)"
-                if world == 1 else ("FusedTPStack (pinned host in/out, one cats_tp_mlp_stack C call per rank)"
-                                    if mega else "TPStack (CUDA graph of kernels + NCCL all-reduce)")},
-        "gpu_launches": args.steps * (1 if mega else stack.launches_per_step),
-        "roofline": roofline, "clocks": clocks.summary(), "dense_cublas": dense,
-        "cpu_baseline": cpu,
+        "data": "synthetic", "config": config_block(args, H, I, dtype, L, s, D.world),
+        "e2e": {"value": B * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
+                "ms_per_step_samples": e2e_samples,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "api": api},
+        "gpu_launches": args.steps * len(head["ms_per_step_samples"]) * launches,
+        "gpu_launches_per_step": launches,
+        "roofline": roofline, "clocks": head["clocks"], "cpu_baseline": cpu,
     }
-    if stats is not None:
-        line["roofline"]["stats_kernels"] = stats
-    if world > 1:
-        line["tp"] = {"mode": tp_mode, "nccl_allreduce_variant": nccl_variant}
+    if "parity" in head:
+        line["parity"] = head["parity"]
+    if D.world > 1:
+        line["tp"] = {"mode": head["mode"],
+                      "nccl_allreduce_variant": head.get("nccl_allreduce_variant")}
+    line.update(extra)
     emit(line)
     leave()
 

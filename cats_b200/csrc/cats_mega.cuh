@@ -203,6 +203,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   int& s_abort = s_ctl[0];
   __shared__ float s_red[32];
   __shared__ int s_cnt[kParts];
+  __shared__ int s_trip;
   __shared__ int s_pref[kMegaMaxGrid];
 
   const int L = A.L, B = A.B, H = A.H, I = A.I, S = A.S, cw = A.cw, NP = A.parts;
@@ -729,11 +730,19 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       // ---- up and down rows of the two halves ----------------------------------------------------
       for (int h = 0; h < NP; ++h) {
         if (ok) ok = mbar_wait_warp(lready_u + 8u * h, l & 1, &s_abort);
-        if (mma_dot) {  // the group loop below needs the same trip count in every warp
+        int cnt;
+        if (mma_dot) {
+          // The group loop below runs a consumer barrier per group, so every warp needs the same
+          // trip count whatever happens: ONE thread decides it (a warp whose wait gave up and a
+          // warp whose wait succeeded would otherwise disagree, and a consumer barrier that some
+          // warps never reach is a dead CTA); `ok` only switches the work off.
+          if (tid == 0) s_trip = (ok && !s_abort) ? s_cnt[h] : 0;
           consumer_bar_sync();
-          ok = !s_abort;
+          cnt = s_trip;
+          ok = ok && !s_abort;
+        } else {
+          cnt = ok ? s_cnt[h] : 0;
         }
-        const int cnt = ok ? s_cnt[h] : 0;
         float* hg = s_hg + (size_t)h * A.cap * BT;
         if (mma_dot) {
           for (int j0 = 0; j0 < cnt; j0 += 8) {

@@ -91,13 +91,16 @@ class CatsSparseSiluMLP(nn.Module):
 
         # activation histograms: 1000 edges = -inf, 998 points on [-1, 1], +inf (ugly_utils.py:826-833)
         self.is_collect_histogram = False
+        # (float32 CPU tensors whatever default device / dtype the model is being built under)
         num_bins = 1000
-        bins = torch.linspace(-1, 1, num_bins - 2)
-        self.histogram_bins = torch.cat([torch.tensor([-torch.inf]), bins, torch.tensor([torch.inf])])
+        f32 = dict(dtype=torch.float32, device="cpu")
+        bins = torch.linspace(-1, 1, num_bins - 2, **f32)
+        self.histogram_bins = torch.cat([torch.tensor([-torch.inf], **f32), bins,
+                                         torch.tensor([torch.inf], **f32)])
         self._dev_hist = {}     # device -> (edges, pre counts, post counts): int64, on that device
-        self.pre_act_hist_counts = torch.zeros(num_bins - 1)
-        self.abs_post_act_hist_counts = torch.zeros(num_bins - 1)
-        self.post_act_hist_counts = torch.zeros(num_bins - 1)
+        self.pre_act_hist_counts = torch.zeros(num_bins - 1, **f32)
+        self.abs_post_act_hist_counts = torch.zeros(num_bins - 1, **f32)
+        self.post_act_hist_counts = torch.zeros(num_bins - 1, **f32)
         self.t = 0
         self.count = 0
         self.agg_sparsity = 0
@@ -140,7 +143,7 @@ class CatsSparseSiluMLP(nn.Module):
         self.dead_percentage = 0
         self.visit_counts = 0
         self.is_collect_histogram = is_collect_histogram
-        self.histogram_counts = torch.zeros(2000)
+        self.histogram_counts = torch.zeros(2000, dtype=torch.float32, device="cpu")
 
     def deactivate_stats(self):
         self.is_stats = False
@@ -179,8 +182,30 @@ class CatsSparseSiluMLP(nn.Module):
         return ops.packed_wdt(self.down_proj.weight)
 
     def _cuda_decode(self, x):
-        return ops.mlp(x, self.gate_proj.weight, self.up_proj.weight, self.packed_down(),
-                       float(self.dead_threshold))
+        """The decode call, ~32 times per token under HF ``generate``: the validated launch state
+        (weights, packed WdT, workspace, argument list) is kept per module and reused while
+        nothing it depends on has changed; a call then costs one output allocation and one
+        C call."""
+        st = self.__dict__.get("_launch")
+        wg, wu, wd = self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight
+        key = (x.shape, x.dtype, x.device, wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
+               wd._version, id(self.wdown_t), torch.cuda.current_stream(x.device).cuda_stream
+               if x.is_cuda else 0)
+        if st is None or st[0] != key or not x.is_contiguous():
+            wdt = self.packed_down()
+            dev, dt, B, H, I = ops._check_mlp_weights(x, wg, wu, wdt)      # raises on misuse
+            ws = ops.get_workspace(dev, H, I)
+            st = (key, ops._lib.lib().cats_mlp, wdt, ws, B, H, I, ops.dtype_code(dt), dev)
+            self.__dict__["_launch"] = st
+        _, fn, wdt, ws, B, H, I, code, dev = st
+        out = torch.empty_like(x)
+        with ops._on(dev):
+            status = fn(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), wdt.data_ptr(), ws.ptr, ws.nbytes,
+                        B, H, I, code, float(self.dead_threshold), out.data_ptr(), ops.OUT_STORE,
+                        None, None, None, 1e-6, key[-1])
+        if status:
+            ops._lib.check(status, "cats_mlp")
+        return out
 
     def forward(self, x, sp_mask: Optional[torch.Tensor] = None):
         if sp_mask is not None:

@@ -51,6 +51,66 @@ def shard_layer(layer: Layer, rank: int, world: int) -> Layer:
                  shard_rows(layer.wdt, rank, world), layer.threshold)
 
 
+def agree(group: Optional[dist.ProcessGroup] = None, **facts) -> None:
+    """Raise on every rank unless all ranks of the group hold the same ``facts`` (hidden size,
+    batch, number of layers, dtype ...).  Ranks that disagree would run a different number of
+    exchanges, or exchanges of different sizes, and block one another until a time-out; this
+    turns that into an immediate error with the differing values named (host side, one
+    all_gather of a small object)."""
+    if not dist.is_initialized() or dist.get_world_size(group) < 2:
+        return
+    mine = {k: str(v) for k, v in facts.items()}
+    everyone = [None] * dist.get_world_size(group)
+    dist.all_gather_object(everyone, mine, group=group)
+    bad = [(r, k, o[k], everyone[0][k]) for r, o in enumerate(everyone) for k in mine
+           if o.get(k) != everyone[0].get(k)]
+    if bad:
+        raise RuntimeError("cats_b200.tp: the ranks do not agree on the stack: " + "; ".join(
+            f"rank {r} has {k}={v}, rank 0 has {v0}" for r, k, v, v0 in bad))
+
+
+class PeerLost(RuntimeError):
+    """A peer did not report in time (it exited, hangs, or never started)."""
+
+
+class PeerHeartbeat:
+    """Host-side liveness of the ranks of a tensor-parallel group through a key-value store
+    (``torch.distributed`` TCPStore / FileStore / HashStore).  Every rank calls ``beat(step)``
+    after finishing a step and ``require(step)`` before launching step ``step + 1``: a rank that
+    left between steps is then discovered on the host, by name, within ``deadline_s`` - before a
+    kernel is launched that would wait for it on the device until its own limit.  No GPU work."""
+
+    def __init__(self, store, rank: int, world: int, deadline_s: float = 5.0,
+                 prefix: str = "cats_tp/alive"):
+        self.store, self.rank, self.world = store, rank, world
+        self.deadline_s, self.prefix = deadline_s, prefix
+
+    def beat(self, step: int) -> None:
+        self.store.set(f"{self.prefix}/{self.rank}", str(int(step)))
+
+    def _seen(self, peer: int) -> int:
+        key = f"{self.prefix}/{peer}"
+        if not self.store.check([key]):
+            return -1
+        return int(self.store.get(key))
+
+    def require(self, step: int) -> None:
+        """Return once every peer has reported ``step`` (or a later one); PeerLost otherwise."""
+        import time
+
+        t_end = time.monotonic() + self.deadline_s
+        waiting = [p for p in range(self.world) if p != self.rank]
+        while waiting:
+            waiting = [p for p in waiting if self._seen(p) < step]
+            if not waiting:
+                return
+            if time.monotonic() > t_end:
+                raise PeerLost(f"cats_b200.tp: rank(s) {waiting} did not report step {step} "
+                               f"within {self.deadline_s} s (rank {self.rank} stops before its "
+                               "next launch)")
+            time.sleep(0.005)
+
+
 def _cuda_local_mlp(x, layer: Layer, out, ws=None):
     from . import ops
 
@@ -75,6 +135,7 @@ class TPStack:
         self.dtype, self.device = self.layers[0].wg.dtype, self.layers[0].wg.device
         self.B, self.eps, self.group = batch, eps, group
         self.local_mlp, self.tail = local_mlp, tail
+        agree(group, layers=self.L, hidden=self.H, batch=batch, dtype=self.dtype)
         z = lambda: torch.zeros((batch, self.H), dtype=self.dtype, device=self.device)
         self.x, self.x_tmp, self.resid, self.partial = z(), z(), z(), z()
         self.graph = None
@@ -190,6 +251,7 @@ class FusedTPStack:
             raise RuntimeError("cats_b200.tp: every layer needs the same number of local rows")
         self.dtype, self.device = self.layers[0].wg.dtype, self.layers[0].wg.device
         self.B, self.eps, self.group = batch, eps, group
+        agree(group, layers=self.L, hidden=self.H, batch=batch, dtype=self.dtype)
         z = lambda: torch.zeros((batch, self.H), dtype=self.dtype, device=self.device)
         self.x, self.resid = z(), z()
         self.ws = ops.Workspace(self.device, self.H, self.I_local)

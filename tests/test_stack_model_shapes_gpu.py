@@ -1,0 +1,144 @@
+"""The persistent kernel and the operator API at the model shapes, against the CPU oracle.
+
+Multi-layer stacks at the shapes the benchmarks run (Mistral-7B and Llama-2-7B MLP, the 70B
+shape), in the schedules those shapes select (three parts per layer, tensor-core dot products
+for batches), each run twice on ONE workspace with different inputs: the grid-barrier counters
+and the accumulator buffers carry over from launch to launch.  Then the reference's operator
+conventions at the batch sizes its own test script uses (flash_gemv/test/test_fuse_gemv_cmp.py:
+312-528: batch 2 throughout, 3 for the Triton-backed names) and batches 8 and 16 at model shape.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cats_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def to_np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _bf16(a):
+    return torch.from_numpy(np.asarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+
+
+ROUND = {torch.float16: np.float16, torch.float32: None, torch.bfloat16: _bf16}
+# a gate value next to the threshold may flip in a later layer once 16-bit storage has rounded
+# the residual differently; bf16 keeps 8 bits
+STACK_TOL = {torch.float32: 1e-3, torch.float16: 2e-2, torch.bfloat16: 5e-2}
+
+
+@pytest.mark.parametrize("H,I,L,B,dt,sparsity", [
+    (4096, 14336, 6, 1, torch.float16, 0.5),    # three parts per layer, the benchmark's schedule
+    (4096, 14336, 3, 4, torch.float16, 0.5),    # tensor-core dot products
+    (4096, 11008, 4, 1, torch.float32, 0.5),
+    (8192, 28672, 2, 1, torch.bfloat16, 0.7),
+    (4096, 14336, 4, 2, torch.bfloat16, 0.9),   # few active rows per CTA
+])
+def test_stack_at_model_shape_twice_on_one_workspace(H, I, L, B, dt, sparsity, cuda_device):
+    from cats_b200 import _lib, synth
+    from cats_b200.stack import CatsMLPStack
+
+    layers = synth.make_stack(L, H, I, dt, cuda_device, 17, sparsity)
+    assert _lib.lib().cats_uses_persistent_kernel(L, B, H, I, {torch.float32: 0, torch.float16: 1,
+                                                               torch.bfloat16: 2}[dt]) == 1
+    stack = CatsMLPStack(layers, batch=B)
+    np_layers = [(to_np(l.wg), to_np(l.wu), to_np(l.wdt).T) for l in layers]
+    thr = [l.threshold for l in layers]
+    for seed in (123, 456):
+        x0 = synth.make_x(B, H, dt, cuda_device, seed).reshape(B, H)
+        stack.set_input(x0)
+        stack.run_device()
+        torch.cuda.synchronize()
+        assert stack.ws.counters()[1] == 0
+        xe, re_, _ = O.mlp_stack(to_np(x0), np_layers, thr, round_to=ROUND[dt])
+        assert O.rel_l2(to_np(stack.resid), re_) <= STACK_TOL[dt], (seed, "resid")
+        assert O.rel_l2(to_np(stack.x), xe) <= STACK_TOL[dt], (seed, "x")
+
+
+@pytest.mark.parametrize("B", [8, 16])
+def test_large_batches_at_model_shape(B, cuda_device):
+    from test_parity_gpu import run_and_check, synth_case
+
+    x, layer = synth_case(4096, 14336, B, torch.float16, 0.5, 40 + B, cuda_device)
+    run_and_check(x, layer.wg, layer.wu, layer.wdt, layer.threshold, f"mistral B={B}")
+
+
+@pytest.mark.parametrize("B", [2, 3, 4])
+def test_operator_conventions_with_batches(B, cuda_device):
+    """x (B, 1, H) for the Triton-backed names, (1, B, .) for the CUDA ops, as in the reference's
+    test script."""
+    import flash_gemv as fg
+    from test_parity_gpu import synth_case
+
+    dev, dt = cuda_device, torch.float16
+    H, I = 1024, 2752
+    x, layer = synth_case(H, I, B, dt, 0.5, 80 + B, dev)          # x: (B, 1, H)
+    thr, wg, wu, wdt = layer.threshold, layer.wg, layer.wu, layer.wdt
+    wd = wdt.t().contiguous()
+    ref = O.dense_masked_mlp(to_np(x).reshape(B, H), to_np(wg), to_np(wu), to_np(wd), thr)
+    ok = lambda t, tol=1e-2: O.rel_l2(to_np(t).reshape(B, -1), ref["out"]) <= tol
+
+    # Triton-backed names: x (B, 1, H), result (B, 1, H)
+    x_1 = torch.nn.functional.silu(torch.nn.functional.linear(x, wg))
+    y = fg.gemv_gemv_triton(x, x_1, wu, wdt, thr)
+    assert y.shape == (B, 1, H) and ok(y, 2e-2)
+    y = fg.flag_gemv_gemv_triton(x, wg.t().contiguous(), wu, wdt, thr)
+    assert y.shape == (B, 1, H) and ok(y)
+
+    # CUDA ops: activations (1, B, H), flags / values (1, B, I)
+    xb = x.reshape(1, B, H).contiguous()
+    val = torch.empty((1, B, I), dtype=dt, device=dev)
+    flag = torch.zeros((1, B, I), dtype=torch.bool, device=dev)
+    for fn in (fg.fuse_gemv_flag_batch, fg.fuse_gemv_flag_local):
+        flag.zero_()
+        fn(xb, wg, val, flag, thr)
+        flips, outside = O.mask_band_check(ref["post_act"], flag.cpu().numpy().reshape(B, I), thr)
+        assert outside == 0
+        assert O.rel_l2(to_np(val).reshape(B, I), ref["post_act"]) <= 5e-3
+    kmask = flag.cpu().numpy().reshape(B, I)
+    exp = O.dense_masked_mlp(to_np(x).reshape(B, H), to_np(wg), to_np(wu), to_np(wd), thr, mask=kmask)
+    fg.fuse_flag_gemv_local(xb, wu, val, flag)                     # in place: gate -> gate * up
+    assert O.rel_l2(to_np(val).reshape(B, I), exp["inter"]) <= 5e-3
+    acc = torch.zeros((1, B, H), dtype=torch.float32, device=dev)
+    fg.atomic_gemv(val, wdt, acc, flag)
+    assert O.rel_l2(to_np(acc).reshape(B, H), exp["out"]) <= 1e-2
+    out = torch.empty((1, B, H), dtype=dt, device=dev)
+    fg.flag_gemv_gemv(xb, wg, wu, wd, out, thr)
+    assert ok(out)
+    acc.zero_()
+    fg.flag_gemv_gemv_atomic(xb, wg, wu, wdt, acc, thr)
+    assert ok(acc)
+    y = fg.flag_gemv_gemv_inner(xb, wg, wu, wd, thr)
+    assert y.shape == xb.shape and ok(y)
+
+
+def test_module_forward_in_a_loop_reuses_its_launch_state(cuda_device):
+    """What HF ``generate`` does to the module: the same decode call many times.  The module's
+    cached launch arguments must follow a changed threshold and a replaced weight."""
+    from cats_b200 import sparse_silu as S
+
+    dt = torch.float16
+    torch.manual_seed(0)
+    m = S.LlamaSparseSiluMLP({"hidden_size": 1024, "intermediate_size": 2752}).to(cuda_device, dt)
+    with torch.no_grad():
+        for lin in (m.gate_proj, m.up_proj, m.down_proj):
+            lin.weight.normal_(0, 0.04)
+    m.is_profile, m.sp_method = True, 1
+    m.dead_threshold = torch.tensor(0.25)
+    with torch.no_grad():
+        for step in range(6):
+            if step == 3:
+                m.dead_threshold = torch.tensor(0.4)
+            if step == 4:
+                m.down_proj.weight.mul_(0.5)                       # in-place update of a weight
+            x = torch.randn(2, 1, 1024, device=cuda_device).to(dt)
+            y = m(x)
+            m.sp_method = 0
+            dense = m(x)
+            m.sp_method = 1
+            assert O.rel_l2(to_np(y), to_np(dense)) <= 3e-2, step

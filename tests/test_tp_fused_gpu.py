@@ -87,6 +87,71 @@ def test_bad_rank_arguments_are_refused_on_the_host(cuda_device):
     assert ws.counters()[1] == 0
 
 
+def test_a_wait_that_runs_out_ends_the_kernel_with_a_status_and_recovery_works(cuda_device):
+    """Rank 0 of a pretended group of two, on one GPU: the second exchange buffer is a local
+    buffer that nobody writes, so rank 0's wait for rank 1's partial sums can only run out.  With
+    the limit set to 50 ms (waits for other ranks get four times that) the kernel must end by
+    itself, leave a non-zero device status, and - after the documented recovery: new exchange
+    buffers, cleared workspace - the next call must be correct.  Nothing faults and nothing
+    spins for ever: this is the bounded-wait path doing its job."""
+    from cats_b200 import _lib, ops, synth, tp
+    from cats_b200.stack import CatsMLPStack
+
+    H, I, L, B, dt = 1024, 2752, 3, 1, torch.float16
+    layers = synth.make_stack(L, H, I, dt, cuda_device, 5, 0.5)
+    x0 = synth.make_x(B, H, dt, cuda_device, 77).reshape(B, H)
+    lib = _lib.lib()
+    ws = ops.Workspace(cuda_device, H, I)
+    own = torch.zeros(lib.cats_tp_exchange_bytes(H), dtype=torch.uint8, device=cuda_device)
+    silent = torch.zeros_like(own)                       # "rank 1": never written by anyone
+    arr = lambda ts: (ctypes.c_void_p * L)(*[t.data_ptr() for t in ts])
+    thr = (ctypes.c_float * L)(*[l.threshold for l in layers])
+    x, resid = x0.clone(), x0.clone()
+    ex = (ctypes.c_void_p * 2)(own.data_ptr(), silent.data_ptr())
+    assert lib.cats_set_option(b"wait_ms", 50) == 0
+    try:
+        import time
+        t0 = time.time()
+        st = lib.cats_tp_mlp_stack(L, arr([l.wg for l in layers]), arr([l.wu for l in layers]),
+                                   arr([l.wdt for l in layers]), thr, x.data_ptr(), resid.data_ptr(),
+                                   ws.ptr, ws.nbytes, B, H, I, _lib.F16, 1e-6, 2, 0, ex,
+                                   torch.cuda.current_stream().cuda_stream)
+        assert st == _lib.OK                              # asynchronous: the launch itself is fine
+        n_active, status = ws.counters()                  # synchronises the stream
+        elapsed = time.time() - t0
+    finally:
+        assert lib.cats_set_option(b"wait_ms", 1000) == 0
+    assert status == 3, status                            # STATUS_WAIT_TIMEOUT_MEGA
+    assert elapsed < 5.0, elapsed                         # ended by itself, well inside a few limits
+    # recovery as documented in include/cats_b200.h: the workspace is cleared, new buffers
+    _lib.check(lib.cats_workspace_init(ws.ptr, ws.nbytes, torch.cuda.current_stream().cuda_stream))
+    fused = tp.FusedTPStack(layers, batch=B)              # fresh exchange buffer, world size 1
+    fused.ws = ws
+    fused.set_input(x0)
+    fused.run_device()
+    torch.cuda.synchronize()
+    assert fused.device_status() == 0
+    plain = CatsMLPStack(layers, batch=B)
+    plain.set_input(x0)
+    plain.run_device()
+    torch.cuda.synchronize()
+    assert O.rel_l2(to_np(fused.resid), to_np(plain.resid)) <= 2e-2
+    fused.close()
+
+
+def test_a_stack_that_saw_a_timeout_refuses_further_launches(cuda_device):
+    from cats_b200 import synth, tp
+
+    layers = synth.make_stack(2, 1024, 2752, torch.float16, cuda_device, 5, 0.5)
+    fused = tp.FusedTPStack(layers, batch=1)
+    fused.ws.buf[8:12].view(torch.int32).fill_(3)         # the status word, as a time-out leaves it
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        fused.check()
+    with pytest.raises(RuntimeError, match="invalid"):
+        fused.run_device()
+    fused.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_ranks_on_two_gpus_match_the_unsharded_oracle():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
