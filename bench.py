@@ -355,6 +355,23 @@ def layer_bytes(layers, n_act, B, H, esize):
     return esize * I_local * H + 2 * esize * n_act * H + 4 * esize * B * H
 
 
+def chain_active_counts(stack, layers, B, H, limit=8):
+    """Active neurons (union over the batch) of the first layers along the real chain: the layers
+    one launch at a time from the stack's current input, with the counter read back after each.
+    For reporting, outside every timed region."""
+    from cats_b200 import ops
+
+    counts = []
+    x, r = stack.x.clone(), stack.resid.clone()
+    nxt = torch.empty_like(x)
+    for l in layers[:limit]:
+        ops.mlp(x.reshape(B, 1, H), l.wg, l.wu, l.wdt, l.threshold, resid=r, x_next=nxt,
+                eps=stack.eps, ws=stack.ws)
+        counts.append(stack.ws.counters()[0])
+        x, nxt = nxt, x
+    return counts
+
+
 def active_counts(layers, x0, B, H, ws, limit=8):
     """Active neurons (union over the batch) of the first layers for the input x0: stage 1 alone
     plus the counter read-back.  For reporting, outside every timed region."""
@@ -470,20 +487,27 @@ def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=
     else:
         stack, mode = build_tp_stack(layers, B, x0, args.tp, D)
         persistent = isinstance(stack, tp.FusedTPStack)
-    stack.set_input(x0)
-    for _ in range(max(3, args.warmup)):
+    def step():
+        # every step decodes the same token state (two 8 KB device copies): the active sets are
+        # then the calibrated ones at every step and n_active below is what the kernel streamed;
+        # without the reset the residual would keep growing from step to step
+        stack.set_input(x0)
         stack.run_device()
+
+    for _ in range(max(3, args.warmup)):
+        step()
     clocks = None
     if sample_clocks:      # SM clock and throttle reasons DURING the timed regions
         with ClockSampler(D.local_rank) as sampler:
-            samples = timed_regions(stack.run_device, args.steps, regions, D, stream)
+            samples = timed_regions(step, args.steps, regions, D, stream)
         clocks = sampler.summary()
     else:
-        samples = timed_regions(stack.run_device, args.steps, regions, D, stream)
+        samples = timed_regions(step, args.steps, regions, D, stream)
     ms = statistics.median(samples)
     if persistent and D.world > 1:
         stack.check()
-    n_act = statistics.mean(active_counts(layers, x0, B, H, stack.ws))
+    stack.set_input(x0)
+    n_act = statistics.mean(chain_active_counts(stack, layers, B, H))
     by = layer_bytes(layers, n_act, B, H, esize)
     peak, peak_src = hbm_peak()
     us_layer = ms * 1e3 / L
@@ -505,9 +529,14 @@ def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=
         ref = tp.TPStack(layers, batch=B)
         ref.set_input(x0)
         ref.capture()
-        for _ in range(3):
+
+        def ref_step():
+            ref.set_input(x0)
             ref.run_device()
-        rs = timed_regions(ref.run_device, max(5, args.steps // 2), 3, D, stream)
+
+        for _ in range(3):
+            ref_step()
+        rs = timed_regions(ref_step, max(5, args.steps // 2), 3, D, stream)
         block["nccl_allreduce_variant"] = {
             "us_per_layer": statistics.median(rs) * 1e3 / L,
             "what": "stage kernels + one NCCL all-reduce + tail per layer, CUDA graph",
@@ -538,7 +567,7 @@ def single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act, esize, pea
     by = esize * I * H + 2 * esize * n_act * H + 4 * esize * B * H
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=xin.device)
     fl = per_launch_us(call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
-    k = int(round(n_act))
+    k = (int(round(n_act)) + 7) // 8 * 8      # whole 16-byte vectors of fp16, as cuBLAS likes them
     dense_call = lambda i: F.linear(F.silu(F.linear(xin, layers[i].wg)) * F.linear(xin, layers[i].wu),
                                     layers[i].wdt.t())
     opt_call = lambda i: F.linear(F.silu(F.linear(xin, layers[i].wg[:k])) * F.linear(xin, layers[i].wu[:k]),

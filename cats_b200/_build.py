@@ -24,6 +24,7 @@ UNITS = [("cats_abi.cu", [], "cats_abi.o")]
 for _id, _name in ((0, "f32"), (1, "f16"), (2, "bf16")):
     UNITS.append(("cats_inst_stage.cu", [f"-DCATS_ELEM_ID={_id}"], f"cats_inst_stage_{_name}.o"))
     UNITS.append(("cats_inst_mega.cu", [f"-DCATS_ELEM_ID={_id}"], f"cats_inst_mega_{_name}.o"))
+UNITS.append(("cats_inst_dense.cu", [], "cats_inst_dense.o"))
 SOURCES = sorted({u[0] for u in UNITS})
 HEADERS = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
     os.path.join(ROOT, "include", "cats_b200.h")]

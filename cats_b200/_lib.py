@@ -47,6 +47,10 @@ SIGNATURES = {
     "cats_mlp": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t,
                           _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_void_p,
                           _c_void_p, _c_void_p, _c_float, _c_void_p]),
+    "cats_mlp_dense": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t,
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_void_p,
+                                _c_void_p, _c_void_p, _c_float, _c_void_p]),
+    "cats_dense_supported": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
     "cats_mlp_static": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_void_p, _c_void_p]),
     "cats_mlp_static_limit": (_c_size_t, []),

@@ -104,6 +104,8 @@ struct Options {
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
   int wait_ms = 1000;  // limit of every device-side wait (mbarrier, grid barrier, peer data)
+  int xchg = 0;        // tensor-parallel exchange: 0 = by the number of ranks, 1 = every CTA adds
+                       // all ranks' partial sums, 2 = per-slice totals published by each CTA
 };
 Options& options() {
   static Options o = [] {
@@ -116,6 +118,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_MMA_DOT")) v.mma_dot = atoi(e);
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
     if (const char* e = getenv("CATS_B200_WAIT_MS")) v.wait_ms = atoi(e);
+    if (const char* e = getenv("CATS_B200_XCHG")) v.xchg = atoi(e);
     return v;
   }();
   return o;
@@ -307,6 +310,33 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   CATS_DISPATCH(dtype, inst_mega, p, P, A, ws, st);
 }
 
+// Dense tensor-core path: one row tile of at most 128 neurons per CTA and pass (two passes at the
+// 70B shape), rings as deep as shared memory allows.
+DensePlan plan_dense(int B, int H, int I, int dtype) {
+  DensePlan p;
+  if (dtype == CATS_F32 || B < 1 || B > 16 || H % 128 || I % 64 || H < 128) return p;
+  p.grid = dev_info().sms;
+  if (p.grid > I / 8) p.grid = I / 8;
+  if (p.grid < 1) return p;
+  const int rows = (I + p.grid - 1) / p.grid;            // most neurons any CTA owns
+  const int tiles = (rows + 127) / 128;
+  const int per_tile = (rows + tiles - 1) / tiles;
+  p.box_rows = (per_tile + 7) / 8 * 8;
+  if (p.box_rows > 128) p.box_rows = 128;
+  const size_t limit = (size_t)dev_info().max_smem_optin - 4096;   // static shared memory + slack
+  const size_t st1 = 2 * 16384 + 2048, st2 = 16384 + 2048;
+  p.S1 = (int)((limit - 1024) / st1);
+  p.S2 = (int)((limit - 1024) / st2);
+  if (p.S1 > 16) p.S1 = 16;
+  if (p.S2 > 16) p.S2 = 16;
+  if (p.S1 < 2 || p.S2 < 2) return p;
+  p.smem1 = p.S1 * st1 + 1024;
+  p.smem2 = p.S2 * st2 + 1024;
+  p.wait_kc = wait_kcycles();
+  p.ok = true;
+  return p;
+}
+
 cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, int dtype,
                     float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
   const TmaPlan p = plan_gate_tma(B, H, I, dtype);
@@ -375,6 +405,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "mma_dot")) options().mma_dot = value;
   else if (!strcmp(name, "parts")) options().parts = value;
   else if (!strcmp(name, "wait_ms")) options().wait_ms = value;
+  else if (!strcmp(name, "xchg")) options().xchg = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }
@@ -498,6 +529,28 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
                                norm_weight, eps, nullptr, st));
 }
 
+int cats_mlp_dense(const void* x, const void* Wg, const void* Wu, const void* Wd, void* ws,
+                   size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
+                   int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
+                   void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (!x || !Wg || !Wu || !Wd) return CATS_ERR_NULL;
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(Wu) || !aligned16(Wd)) return CATS_ERR_ALIGN;
+  if ((s = check_out_mode(out_mode, out, resid, x_next))) return s;
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  const DensePlan dp = plan_dense(B, H, I, dtype);
+  if (!dp.ok) return CATS_ERR_MODE;
+  return cuda_status(inst_dense(dp, x, Wg, Wu, Wd, p, B, H, I, dtype, threshold, out, out_mode, resid,
+                                x_next, norm_weight, eps, static_cast<cudaStream_t>(stream)));
+}
+
+int cats_dense_supported(int B, int H, int I, int dtype) {
+  if (check_common(B, H, I, dtype)) return 0;
+  return plan_dense(B, H, I, dtype).ok ? 1 : 0;
+}
+
 int cats_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const void* const* WdT,
                    const float* thresholds, void* x_io, void* x_tmp, void* resid, void* ws,
                    size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream) {
@@ -618,6 +671,8 @@ int cats_tp_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const
   A.L = L; A.B = B; A.H = H; A.I = I_local; A.eps = eps;
   A.x_in = x_io; A.x_out = x_io; A.resid = resid; A.out_last = nullptr;
   A.nranks = nranks; A.rank = rank;
+  // up to two ranks a CTA reads at most twice what the totals would be and saves a hand-off
+  A.xchg_all = options().xchg == 1 ? 1 : options().xchg == 2 ? 0 : (nranks <= 2 ? 1 : 0);
   for (int q = 0; q < nranks; ++q) A.xchg[q] = static_cast<unsigned char*>(exchange[q]);
   return cuda_status(do_mega(mp, P, A, p, dtype, static_cast<cudaStream_t>(stream)));
 }

@@ -87,6 +87,7 @@ struct MegaArgs {
   // their own row slice and exchange the layers' partial sums through `xchg` (xchg[p] = rank
   // p's exchange buffer as mapped into this process; xchg[rank] is local).  nranks == 0: none.
   int nranks, rank;
+  int xchg_all;  // 1: every CTA adds all ranks' slots itself; 0: per-slice totals (see the lister)
   unsigned char* xchg[kMaxRanks];
 };
 
@@ -455,10 +456,11 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         // CTA's slice of the sums to every rank's slot for this rank (plain stores of (value,
         // tag) pairs into peer memory) and clear the slice for layer l+2 (nobody else reads the
         // accumulators in this mode; the clearing reaches the other CTAs through the list and
-        // layer barriers of layer l+1).  Then add the ranks' partial sums of the same slice as
-        // they arrive in this GPU's slots - in rank order, so every rank computes bit-identical
-        // totals - and publish the total, tagged again, for all CTAs of this GPU: a CTA reads
-        // B * H totals per layer instead of nranks * B * H partial sums.
+        // layer barriers of layer l+1).  Then (unless every CTA reads all ranks' slots itself,
+        // A.xchg_all) add the ranks' partial sums of the same slice as they arrive in this GPU's
+        // slots - in rank order, so every rank computes bit-identical totals - and publish the
+        // total, tagged again, for all CTAs of this GPU: a CTA then reads B * H totals per layer
+        // instead of nranks * B * H partial sums, at the price of one more hand-off through L2.
         if (ok) ok = grid_wait(obar, otarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
@@ -480,15 +482,28 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
           }
           bool good = true;
-          for (int e = lane; e < B * own_n; e += 32) {
+          for (int e = lane; e < B * own_n && !A.xchg_all; e += 32) {
             const int b = e / own_n, g = own_lo + (e - b * own_n);
+            const uint2* src0 = xchg_slot(A.xchg[A.rank], set, 0, H) + (size_t)b * H + 4 * (size_t)g;
+            const size_t sstride = (size_t)kMegaMaxB * H;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int p = 0; p < K && good; ++p) {
-              unsigned long long u[4];
-              good = ld_group_tagged(xchg_slot(A.xchg[A.rank], set, p, H) + (size_t)b * H +
-                                         4 * (size_t)g, tag, &s_abort, u);
-              a.x += pair_val(u[0]); a.y += pair_val(u[1]);
-              a.z += pair_val(u[2]); a.w += pair_val(u[3]);
+            for (int p0 = 0; p0 < K && good; p0 += 4) {  // four sources' loads in flight at a time
+              unsigned long long u[4][4];
+#pragma unroll
+              for (int pp = 0; pp < 4; ++pp)
+                if (p0 + pp < K) {
+                  ld_pairs(src0 + (p0 + pp) * sstride, u[pp][0], u[pp][1]);
+                  ld_pairs(src0 + (p0 + pp) * sstride + 2, u[pp][2], u[pp][3]);
+                }
+#pragma unroll
+              for (int pp = 0; pp < 4; ++pp)
+                if (p0 + pp < K && good) {
+                  if (!(pair_has(u[pp][0], tag) && pair_has(u[pp][1], tag) &&
+                        pair_has(u[pp][2], tag) && pair_has(u[pp][3], tag)))
+                    good = ld_group_tagged(src0 + (p0 + pp) * sstride, tag, &s_abort, u[pp]);
+                  a.x += pair_val(u[pp][0]); a.y += pair_val(u[pp][1]);
+                  a.z += pair_val(u[pp][2]); a.w += pair_val(u[pp][3]);
+                }
             }
             if (good) {
               uint2* dst = xchg_sums(A.xchg[A.rank], set, H) + (size_t)b * H + 4 * (size_t)g;
@@ -532,7 +547,13 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       consumer_bar_sync();
       ok = !s_abort;
       const float* accp = ws.acc32 + (size_t)(l & 1) * kMaxB * H;
-      const uint2* sums = K ? xchg_sums(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), H) : nullptr;
+      // tensor parallel: nsrc arrays of tagged pairs to add in order - the ranks' slots
+      // (A.xchg_all) or the one array of totals that the listers publish
+      const int nsrc = K ? (A.xchg_all ? K : 1) : 0;
+      const uint2* srcs = !K ? nullptr
+                          : A.xchg_all ? xchg_slot(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), 0, H)
+                                       : xchg_sums(A.xchg[A.rank], (int)((xl0 + (unsigned)l) & 1u), H);
+      const size_t sstride = (size_t)kMegaMaxB * H;
       const unsigned tag = xl0 + (unsigned)l + 1u;
       const int ngrp = ngrp_all;
       const T* nw = reinterpret_cast<const T*>(P.nw[l]);
@@ -549,30 +570,32 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
                                 : make_float4(0.f, 0.f, 0.f, 0.f);
             }
           } else {
-            // all loads first (one L2 round trip when everything has arrived), then the checks;
-            // a group whose pairs are not all there yet is read again on its own
-            unsigned long long u[KV][4];
 #pragma unroll
-            for (int q = 0; q < KV; ++q) {
-              const int g = g0 + q * kConsumerThreads + tid;
-              if (g < ngrp) {
-                const uint2* src = sums + (size_t)b * H + 4 * (size_t)g;
-                ld_pairs(src, u[q][0], u[q][1]);
-                ld_pairs(src + 2, u[q][2], u[q][3]);
+            for (int q = 0; q < KV; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < nsrc; ++p) {
+              // all loads first (one L2 round trip when everything has arrived), then the checks;
+              // a group whose pairs are not all there yet is read again on its own
+              const uint2* sp = srcs + p * sstride + (size_t)b * H;
+              unsigned long long u[KV][4];
+#pragma unroll
+              for (int q = 0; q < KV; ++q) {
+                const int g = g0 + q * kConsumerThreads + tid;
+                if (g < ngrp) {
+                  ld_pairs(sp + 4 * (size_t)g, u[q][0], u[q][1]);
+                  ld_pairs(sp + 4 * (size_t)g + 2, u[q][2], u[q][3]);
+                }
               }
-            }
 #pragma unroll
-            for (int q = 0; q < KV; ++q) {
-              const int g = g0 + q * kConsumerThreads + tid;
-              a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (g < ngrp) {
-                bool good = pair_has(u[q][0], tag) && pair_has(u[q][1], tag) &&
-                            pair_has(u[q][2], tag) && pair_has(u[q][3], tag);
-                if (!good && ok)
-                  good = ld_group_tagged(sums + (size_t)b * H + 4 * (size_t)g, tag, &s_abort, u[q]);
-                if (!good) ok = false;
-                a[q] = make_float4(pair_val(u[q][0]), pair_val(u[q][1]), pair_val(u[q][2]),
-                                   pair_val(u[q][3]));
+              for (int q = 0; q < KV; ++q) {
+                const int g = g0 + q * kConsumerThreads + tid;
+                if (g < ngrp) {
+                  bool good = pair_has(u[q][0], tag) && pair_has(u[q][1], tag) &&
+                              pair_has(u[q][2], tag) && pair_has(u[q][3], tag);
+                  if (!good && ok) good = ld_group_tagged(sp + 4 * (size_t)g, tag, &s_abort, u[q]);
+                  if (!good) ok = false;
+                  a[q].x += pair_val(u[q][0]); a[q].y += pair_val(u[q][1]);
+                  a[q].z += pair_val(u[q][2]); a[q].w += pair_val(u[q][3]);
+                }
               }
             }
           }

@@ -100,6 +100,8 @@ class CatsDecoder:
         self.h = z(batch, self.H)                       # residual stream of the current token
         self.x = z(batch, self.H)                       # normalised input of the next block
         self.x2 = z(batch, self.H)
+        self.attn = z(batch, self.H)
+        self.logits = z(batch, cfg.vocab_size)          # logits of the latest step (static buffer)
         self.ar = torch.arange(self.max_len, device=self.dev)
         self.out_tokens: List[torch.Tensor] = []
         self.graphs = {}
@@ -115,19 +117,17 @@ class CatsDecoder:
         self.mlp_launches_per_step = self.L if mlp == "cats" else 0
 
     # ---- pieces ---------------------------------------------------------------------------------
-    def _attn_decode(self, l: int, x: torch.Tensor, bucket: int) -> torch.Tensor:
+    def _attn_decode(self, l: int, x: torch.Tensor, bucket: int, cos, sin, mask) -> torch.Tensor:
         B, nh, nkv, hd = self.B, self.nh, self.nkv, self.hd
         qkv = F.linear(x, self.wqkv[l])
         q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], -1)
-        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)  # [1, hd]
         q, k = q.view(B, nh, hd), k.view(B, nkv, hd)
         q = q * cos + _rotate_half(q) * sin
         k = k * cos + _rotate_half(k) * sin
         self.kc[l].index_copy_(2, self.pos, k.unsqueeze(2))
         self.vc[l].index_copy_(2, self.pos, v.reshape(B, nkv, 1, hd))
-        mask = torch.where(self.ar[:bucket] <= self.pos, 0.0, float("-inf")).to(self.dt)
         o = F.scaled_dot_product_attention(q.unsqueeze(2), self.kc[l][:, :, :bucket],
-                                           self.vc[l][:, :, :bucket], attn_mask=mask.view(1, 1, 1, bucket),
+                                           self.vc[l][:, :, :bucket], attn_mask=mask,
                                            enable_gqa=nh != nkv)
         return F.linear(o.reshape(B, nh * hd), self.wo[l])
 
@@ -149,21 +149,35 @@ class CatsDecoder:
         p = F.silu(F.linear(self.x2, self.wg[l]))
         if self.mode == "masked":
             p = torch.where(p.abs() <= self.thr[l], torch.zeros_like(p), p)
-        self.h.add_(F.linear(p * F.linear(self.x2, self.wu[l]), self.wd[l]))
-        self.x.copy_(_rmsnorm(self.h, nw, self.eps))
+        y = F.linear(p * F.linear(self.x2, self.wu[l]), self.wd[l])
+        if self.dev.type == "cuda":
+            ops.tail(y, self.h, self.x, nw, self.eps)
+        else:
+            self.h.add_(y)
+            self.x.copy_(_rmsnorm(self.h, nw, self.eps))
 
+    @torch.no_grad()
     def _step(self, bucket: int) -> None:
         """One decode step on device state: consumes self.tok at self.pos, leaves the next token
         in self.tok and advances self.pos."""
         self.h.copy_(self.embed.index_select(0, self.tok))
         self.x.copy_(_rmsnorm(self.h, self.ln1[0], self.eps))
+        # position-dependent pieces once per step, not once per layer
+        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)  # [1, hd]
+        mask = torch.where(self.ar[:bucket] <= self.pos, 0.0, float("-inf")).to(self.dt)
+        mask = mask.view(1, 1, 1, bucket)
         for l in range(self.L):
-            self.h.add_(self._attn_decode(l, self.x, bucket))
-            self.x2.copy_(_rmsnorm(self.h, self.ln2[l], self.eps))
+            a = self._attn_decode(l, self.x, bucket, cos, sin, mask)
+            if self.dev.type == "cuda":
+                # h += attn; x2 = rmsnorm(h) * ln2 in one launch (cats_tail, the same kernel in
+                # every mlp mode, so the comparison between the modes stays about the MLP)
+                ops.tail(a, self.h, self.x2, self.ln2[l], self.eps)
+            else:
+                self.h.add_(a)
+                self.x2.copy_(_rmsnorm(self.h, self.ln2[l], self.eps))
             self._mlp_tail(l)
-        logits = F.linear(self.x, self.lm_head)
-        self.logits = logits
-        self.tok.copy_(logits.argmax(-1))
+        torch.matmul(self.x, self.lm_head.t(), out=self.logits)
+        self.tok.copy_(self.logits.argmax(-1))
         self.pos.add_(1)
 
     # ---- prefill ----------------------------------------------------------------------------------

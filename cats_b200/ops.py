@@ -291,6 +291,55 @@ def mlp(x, wg, wu, wdt, threshold: float, out: Optional[torch.Tensor] = None,
     return out
 
 
+# Smallest batch that cats_b200 routes to the dense tensor-core path when the caller holds
+# down_proj.weight in its nn.Linear layout (module, decoder, flash_gemv's *_inner names).  With
+# independent masks at 50 % the union of four tokens' active sets is 94 % of the neurons.
+DENSE_MIN_BATCH = 3
+
+
+def dense_supported(B: int, H: int, I: int, dtype: torch.dtype) -> bool:
+    """Whether ``mlp_dense`` can run this shape (16-bit weights, H % 128 == 0, I % 64 == 0)."""
+    if dtype not in (torch.float16, torch.bfloat16):
+        return False
+    return _lib.lib().cats_dense_supported(B, H, I, dtype_code(dtype)) == 1
+
+
+def mlp_dense(x, wg, wu, wd, threshold: float, out: Optional[torch.Tensor] = None, resid=None,
+              x_next=None, norm_weight=None, eps: float = 1e-6,
+              ws: Optional[Workspace] = None) -> torch.Tensor:
+    """The CATS MLP for a batch on the tensor cores (``cats_mlp_dense``): every weight row is
+    streamed, each token's own mask ``|SiLU(gate)| > threshold`` is applied to its products.
+    x (B,H)/(B,1,H)/(1,B,H); wg, wu (I, H); wd (H, I) = down_proj.weight as nn.Linear stores it."""
+    _req(x, "input")
+    dev, dt = x.device, x.dtype
+    B, H = batch_of(x)
+    _check_batch(B)
+    _req(wg, "gate weight", dt, dev)
+    _req(wu, "up weight", dt, dev)
+    _req(wd, "down weight (H, I)", dt, dev)
+    I = wg.shape[0]
+    if tuple(wg.shape) != (I, H) or tuple(wu.shape) != (I, H) or tuple(wd.shape) != (H, I):
+        raise RuntimeError(f"cats_b200: expected gate/up ({I}, {H}) and down ({H}, {I}), got "
+                           f"{tuple(wg.shape)}, {tuple(wu.shape)}, {tuple(wd.shape)}")
+    if out is None and resid is None:
+        out = torch.empty_like(x)
+    for t, name in ((out, "output"), (resid, "resid"), (x_next, "x_next")):
+        if t is not None:
+            _req(t, name, dt, dev)
+            if t.numel() != B * H:
+                raise RuntimeError(f"cats_b200: {name} must hold B*H elements")
+    if norm_weight is not None:
+        _req(norm_weight, "norm weight", dt, dev)
+    ws = ws or get_workspace(dev, H, I)
+    with _on(dev):
+        _lib.check(_lib.lib().cats_mlp_dense(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
+                                             ws.ptr, ws.nbytes, B, H, I, dtype_code(dt),
+                                             float(threshold), _ptr(out), OUT_STORE, _ptr(resid),
+                                             _ptr(x_next), _ptr(norm_weight), float(eps),
+                                             _stream(dev)), "cats_mlp_dense")
+    return out
+
+
 def down_dense(inter: torch.Tensor, wd: torch.Tensor, out: Optional[torch.Tensor] = None):
     """Dense down projection over Wd (H, I) (``cats_down_dense``); inter holds B*I elements."""
     _req(inter, "intermediate")

@@ -75,9 +75,13 @@ int cats_sm_count(void);
  * "parts" (0 = automatic, or 1..3 parts per layer).  "wait_ms": limit of every wait inside a
  * kernel (on a shared-memory barrier, a grid barrier, another rank's data), default 1000; a wait
  * that runs out makes the kernel leave in an orderly way and sets the device status word (see
- * cats_read_counters); waits for other ranks get four times the limit.  The same values are read
+ * cats_read_counters); waits for other ranks get four times the limit.  "xchg": how the ranks'
+ * partial sums are combined in cats_tp_mlp_stack (0 = chosen by the number of ranks, 1 = every
+ * CTA adds all ranks' partial sums, 2 = every CTA adds its own slice and publishes the total;
+ * all ranks must use the same value).  The same values are read
  * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
- * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS and CATS_B200_WAIT_MS.
+ * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS, CATS_B200_WAIT_MS
+ * and CATS_B200_XCHG.
  * No reference counterpart (the reference has no device-side waits; its error path is exit(-1),
  * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:25-33, 2397-2400).
  */
@@ -164,6 +168,28 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
              size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
              int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
              void* stream);
+
+/*
+ * The CATS MLP for batches, on the tensor cores: all of Wg, Wu and Wd are streamed once (TMA into
+ * shared memory, tcgen05.mma with the accumulators in tensor memory) and every token's own mask
+ * |SiLU(gate)| > threshold is applied to its own products, the rule of the reference's batched
+ * kernels (fuse_gemv_cmp_cuda.cu:1542-1548).  For batches whose tokens' active sets together cover
+ * (nearly) every neuron - with independent masks at 50 % that is any batch from about four up -
+ * nothing is left to skip and this is the fastest way through the weights; cats_mlp remains the
+ * path for one token and for batches with strongly overlapping masks.
+ *   Wd [H, I]: down_proj.weight as nn.Linear stores it, the layout flag_gemv_gemv_inner* receive
+ *   (flash_gemv/flash_gemv/flash_gemv.py:36-43); Wg, Wu [I, H]; everything else as for cats_mlp.
+ * fp16 / bf16 only (fp32 weights would have to go through tf32), H a multiple of 128, I a
+ * multiple of 64, B <= 16: otherwise CATS_ERR_MODE (cats_dense_supported tells beforehand) and the
+ * caller uses cats_mlp.  gate * up is rounded to the storage type between the two GEMMs, as the
+ * reference's stage 2 hands it to its stage 3.
+ * Replaces the B in {2, 8, 16} launches of flag_gemv_gemv_inner* (fuse_gemv_cmp_cuda.cu:2368-2400).
+ */
+int cats_mlp_dense(const void* x, const void* Wg, const void* Wu, const void* Wd, void* ws,
+                   size_t ws_bytes, int B, int H, int I, int dtype, float threshold, void* out,
+                   int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
+                   void* stream);
+int cats_dense_supported(int B, int H, int I, int dtype);
 
 /*
  * cats_mlp for callers that are not able to allocate device memory.

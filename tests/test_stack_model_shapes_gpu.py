@@ -27,15 +27,43 @@ def _bf16(a):
 
 
 ROUND = {torch.float16: np.float16, torch.float32: None, torch.bfloat16: _bf16}
-# a gate value next to the threshold may flip in a later layer once 16-bit storage has rounded
-# the residual differently; bf16 keeps 8 bits
-STACK_TOL = {torch.float32: 1e-3, torch.float16: 2e-2, torch.bfloat16: 5e-2}
+# Stacks of random layers amplify a perturbation by a factor of about two per layer (one 16-bit
+# rounding of the residual that goes the other way, one gate value that lands on the other side
+# of the threshold), so against the CPU oracle only fp32 storage supports a tight bound over
+# several layers.  16-bit stacks are therefore checked two ways: tightly against the SAME layers
+# run one launch per layer (cats_mlp with the fused tail: identical arithmetic, only the order of
+# the split-K sums differs, so whatever the multi-layer launch adds - barriers between layers,
+# buffers that alternate, lists that carry over - shows up undiluted), and loosely against the
+# oracle (gross errors).  Single launches are held to the oracle's tight bound in test_parity_gpu.
+ORACLE_TOL = {torch.float32: 1e-3, torch.float16: 8e-2, torch.bfloat16: 3e-1}
+CHAIN_BASE = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1e-2}
+
+
+def chain_tol(dt, L):
+    """fp32: flat (1e-5 held over six layers when measured).  16-bit: the bound of two layers,
+    doubled per further layer (measured: 1.1e-2 after six fp16 layers)."""
+    return CHAIN_BASE[dt] if dt == torch.float32 else CHAIN_BASE[dt] * 2 ** max(0, L - 1)
+
+
+def chain_of_single_launches(layers, x0, B, H, eps=1e-6):
+    from cats_b200 import ops
+
+    x, r = x0.clone(), x0.clone()
+    nxt = torch.empty_like(x)
+    for l in layers:
+        ops.mlp(x.reshape(B, 1, H), l.wg, l.wu, l.wdt, l.threshold, resid=r, x_next=nxt, eps=eps)
+        x, nxt = nxt, x
+    return x, r
 
 
 @pytest.mark.parametrize("H,I,L,B,dt,sparsity", [
-    (4096, 14336, 6, 1, torch.float16, 0.5),    # three parts per layer, the benchmark's schedule
+    (4096, 14336, 6, 1, torch.float32, 0.5),    # three parts per layer, tight against the oracle
+    (4096, 14336, 6, 1, torch.float16, 0.5),    # the benchmark's schedule
+    (4096, 14336, 2, 1, torch.float16, 0.5),    # two layers: the tightest 16-bit bound
+    (4096, 14336, 2, 1, torch.bfloat16, 0.5),
     (4096, 14336, 3, 4, torch.float16, 0.5),    # tensor-core dot products
     (4096, 11008, 4, 1, torch.float32, 0.5),
+    (4096, 11008, 3, 2, torch.float32, 0.5),
     (8192, 28672, 2, 1, torch.bfloat16, 0.7),
     (4096, 14336, 4, 2, torch.bfloat16, 0.9),   # few active rows per CTA
 ])
@@ -55,9 +83,12 @@ def test_stack_at_model_shape_twice_on_one_workspace(H, I, L, B, dt, sparsity, c
         stack.run_device()
         torch.cuda.synchronize()
         assert stack.ws.counters()[1] == 0
+        xc, rc = chain_of_single_launches(layers, x0, B, H)
+        assert O.rel_l2(to_np(stack.resid), to_np(rc)) <= chain_tol(dt, L), (seed, "resid vs chain")
+        assert O.rel_l2(to_np(stack.x), to_np(xc)) <= chain_tol(dt, L), (seed, "x vs chain")
         xe, re_, _ = O.mlp_stack(to_np(x0), np_layers, thr, round_to=ROUND[dt])
-        assert O.rel_l2(to_np(stack.resid), re_) <= STACK_TOL[dt], (seed, "resid")
-        assert O.rel_l2(to_np(stack.x), xe) <= STACK_TOL[dt], (seed, "x")
+        assert O.rel_l2(to_np(stack.resid), re_) <= ORACLE_TOL[dt], (seed, "resid")
+        assert O.rel_l2(to_np(stack.x), xe) <= ORACLE_TOL[dt], (seed, "x")
 
 
 @pytest.mark.parametrize("B", [8, 16])
