@@ -482,7 +482,7 @@ def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=
         parity = parity_block(full, x0, B, H, dtype, D, tol)
         del full
     if D.world == 1:
-        stack, mode = CatsMLPStack(layers, batch=B), "single GPU"
+        stack, mode = CatsMLPStack(layers, batch=B, sparsity=s), "single GPU"
         persistent = stack.launches_per_step == 1
     else:
         stack, mode = build_tp_stack(layers, B, x0, args.tp, D)
@@ -521,6 +521,16 @@ def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=
         "n_active_mean_per_rank": n_act, "intermediate_local": layers[0].wg.shape[0],
         "kernel": "k_cats_mega" if persistent else "staged kernels",
     }
+    if D.world == 1 and stack.dense:
+        # dense tensor-core path: every row of the three matrices is streamed
+        streamed = 3 * esize * layers[0].wg.shape[0] * H + 4 * esize * B * H
+        block.update({"kernel": "k_dense_mlp (tcgen05, one cooperative launch per layer, CUDA graph)",
+                      "bytes_streamed_per_layer": streamed,
+                      "GBps_streamed": streamed / us_layer / 1e3,
+                      "frac_of_peak_streamed": streamed / us_layer / 1e3 / peak,
+                      "note": "bytes_per_layer_per_rank / frac_of_peak count the union's bytes "
+                              "(all of Wg + the union's rows of Wu and Wd), *_streamed all three "
+                              "matrices, which is what this path reads"})
     if parity is not None:
         block["parity"] = parity
     if clocks is not None:
@@ -756,6 +766,7 @@ def run_gpu_arm(args):
                                             regions=args.regions, sample_clocks=True,
                                             parity_layers=min(3, L) if not args.no_parity else 0)
     ms_step, us_layer = head["ms_per_step"], head["us_per_layer"]
+    dense_path = D.world == 1 and stack.dense
     I_local = head["intermediate_local"]
     persistent = head["kernel"] == "k_cats_mega"
 
@@ -791,7 +802,7 @@ def run_gpu_arm(args):
     xin = x0.reshape(B, 1, H).clone()
     out = torch.empty_like(xin)
     staged = None
-    if B <= 4:
+    if B <= 4 and not dense_path:
         reps = max(1, min(10, 320 // L))
         gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
                                 L, reps, stream)
@@ -803,7 +814,10 @@ def run_gpu_arm(args):
             "k_updown_tma": {"us": updown_us[0], "bytes": bytes_updown,
                              "GBps": bytes_updown / updown_us[0] / 1e3},
         }
-    if persistent:
+    if D.world == 1 and stack.dense:
+        streamed = head["bytes_streamed_per_layer"]
+        kname, launch_us, launch_bytes = "k_dense_mlp", us_layer, streamed
+    elif persistent:
         kname, launch_us, launch_bytes = "k_cats_mega", ms_step * 1e3, bytes_layer * L
     elif staged:
         kname = max(staged, key=lambda k: staged[k]["us"])
@@ -820,7 +834,8 @@ def run_gpu_arm(args):
         "bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
         "bytes_per_launch": launch_bytes, "launch_us": launch_us,
-        "units_per_launch": f"{L} layers" if persistent else "1 layer stage",
+        "units_per_launch": ("1 layer" if (D.world == 1 and stack.dense) else
+                             f"{L} layers" if persistent else "1 layer stage"),
         "frac_of_8TBps_nominal": achieved / 8000.0,
         "layer": {"bytes": bytes_layer, "us": us_layer, "GBps": bytes_layer / us_layer / 1e3,
                   "frac": bytes_layer / us_layer / 1e3 / peak,
@@ -831,7 +846,7 @@ def run_gpu_arm(args):
     extra = {}
     if D.world == 1 and not args.no_dense:
         # ---- one layer per launch: what a decoder sees, and the reference's protocol ------------
-        if B <= 4:
+        if B <= 4 and not dense_path:
             extra["single_layer"] = single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act,
                                                        esize, peak)
         # ---- statistics kernel beside the path (threshold calibration): HBM-bound stream --------
@@ -905,7 +920,7 @@ def run_gpu_arm(args):
         res = time_cpu(H, I, L, s, B, args.seed, args.cpu_sample_layers, seconds=args.cpu_seconds)
         cpu = cpu_baseline_block(res, L, H, I, B)
 
-    launches = 1 if persistent else 2 * L
+    launches = L if (D.world == 1 and dense_path) else 1 if persistent else 2 * L
     line = {
         "metric": METRIC, "value": B * 1e3 / ms_step, "unit": UNIT, "n_gpus": D.world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,

@@ -104,6 +104,7 @@ struct Options {
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
   int wait_ms = 1000;  // limit of every device-side wait (mbarrier, grid barrier, peer data)
+  int dense_fused = 1; // dense tensor-core path as one cooperative launch (0: two launches)
   int xchg = 0;        // tensor-parallel exchange: 0 = by the number of ranks, 1 = every CTA adds
                        // all ranks' partial sums, 2 = per-slice totals published by each CTA
 };
@@ -119,6 +120,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
     if (const char* e = getenv("CATS_B200_WAIT_MS")) v.wait_ms = atoi(e);
     if (const char* e = getenv("CATS_B200_XCHG")) v.xchg = atoi(e);
+    if (const char* e = getenv("CATS_B200_DENSE_FUSED")) v.dense_fused = atoi(e);
     return v;
   }();
   return o;
@@ -332,6 +334,11 @@ DensePlan plan_dense(int B, int H, int I, int dtype) {
   if (p.S1 < 2 || p.S2 < 2) return p;
   p.smem1 = p.S1 * st1 + 1024;
   p.smem2 = p.S2 * st2 + 1024;
+  const size_t stf = 2 * 16384 + 4096;
+  p.Sf = (int)((limit - 1024) / stf);
+  if (p.Sf > 16) p.Sf = 16;
+  p.smemf = p.Sf * stf + 1024;
+  p.fused = (options().dense_fused && p.Sf >= 2 && p.grid <= dev_info().sms) ? 1 : 0;
   p.wait_kc = wait_kcycles();
   p.ok = true;
   return p;
@@ -406,6 +413,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "parts")) options().parts = value;
   else if (!strcmp(name, "wait_ms")) options().wait_ms = value;
   else if (!strcmp(name, "xchg")) options().xchg = value;
+  else if (!strcmp(name, "dense_fused")) options().dense_fused = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }

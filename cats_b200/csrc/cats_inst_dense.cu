@@ -88,6 +88,27 @@ cudaError_t launch_dense(const DensePlan& p, const void* x, const void* Wg, cons
       !tensor_map(x, B, H, kDenseN, dtype, &m_x) || !tensor_map(Wd, H, I, 128, dtype, &m_wd) ||
       !tensor_map(h, B, I, kDenseN, dtype, &m_h))
     return cudaErrorInvalidValue;
+  if (p.fused) {
+    // one cooperative launch: the CTAs wait for one another at grid barriers
+    auto kernel = k_dense_mlp<T>;
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smemf);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.dynamicSmemBytes = p.smemf;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, m_wg, m_wu, m_x, m_wd, m_h, ws, B, H, I, thr, h, p.box_rows,
+                              (T*)out, out_mode, (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.Sf,
+                              p.wait_kc);
+  }
   cudaError_t e = launch(k_dense_gateup<T>, dim3(p.grid), dim3(kDenseThreads), p.smem1, st, m_wg, m_wu, m_x,
                          ws, B, H, I, thr, h, p.box_rows, p.S1, p.wait_kc);
   if (e != cudaSuccess) return e;

@@ -119,39 +119,6 @@ __host__ __device__ inline int half_row0(int h, int I, int parts) {
   return (int)(((long long)I * h) / parts);
 }
 
-// ---- grid barrier on a monotonic counter ------------------------------------------------------
-// Arrival with release semantics at GPU scope.  It is always executed by lane 0 of a warp right
-// after __syncwarp(), and everything the arrival publishes was written by lanes of that same
-// warp, so this one fence is the only one on the path (an explicit __threadfence() by every
-// writer plus a release here would pay the fence twice, and a fence costs microseconds while
-// the copy ring saturates HBM).
-__device__ __forceinline__ void grid_arrive(unsigned* ctr) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded spin until the counter has reached `target` (wrap-safe compare).
-__device__ __forceinline__ bool grid_wait(const unsigned* ctr, unsigned target,
-                                          volatile int* abort) {
-  if ((int)(ld_acquire_gpu(ctr) - target) >= 0) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-      if ((int)(ld_acquire_gpu(ctr) - target) >= 0) return true;
-      __nanosleep(40);
-    }
-    if (*abort) return false;
-    if (clock64() - t0 > wait_limit(abort)) {
-      *abort = 1;
-      return false;
-    }
-  }
-}
-
 // Two (value, tag) pairs = 16 bytes, each pair one 64-bit element.  System scope: the slots are
 // written by other GPUs over NVLink (and read from this GPU's own memory); the sums are local
 // but share the code.

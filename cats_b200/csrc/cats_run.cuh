@@ -80,8 +80,8 @@ struct MegaPlan {
 // dense tensor-core path (cats_dense.cuh): 16-bit types, H a multiple of 128, I a multiple of 64
 struct DensePlan {
   bool ok = false;
-  int grid = 0, box_rows = 0, S1 = 0, S2 = 0, wait_kc = 0;
-  size_t smem1 = 0, smem2 = 0;
+  int grid = 0, box_rows = 0, S1 = 0, S2 = 0, Sf = 0, wait_kc = 0, fused = 0;
+  size_t smem1 = 0, smem2 = 0, smemf = 0;
 };
 cudaError_t inst_dense(const DensePlan& p, const void* x, const void* Wg, const void* Wu, const void* Wd,
                        WsPtrs ws, int B, int H, int I, int dtype, float thr, void* out, int out_mode,

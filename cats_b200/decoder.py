@@ -115,6 +115,12 @@ class CatsDecoder:
             for w in self.wg + self.wu + self.wdt:
                 ops._req(w, "MLP weight", self.dt, self.dev)
         self.mlp_launches_per_step = self.L if mlp == "cats" else 0
+        # batches: the density-aware switch to the dense tensor-core path (down_proj.weight is
+        # at hand in its native layout)
+        self.dense = (mlp == "cats" and ops.use_dense(batch, getattr(self.mlps[0], "sparsity_level", None))
+                      and ops.dense_supported(batch, self.H, self.I, self.dt))
+        if self.dense:
+            self._fn_dense = _lib.lib().cats_mlp_dense
 
     # ---- pieces ---------------------------------------------------------------------------------
     def _attn_decode(self, l: int, x: torch.Tensor, bucket: int, cos, sin, mask) -> torch.Tensor:
@@ -137,6 +143,15 @@ class CatsDecoder:
     def _mlp_tail(self, l: int) -> None:
         """h += mlp(x2); x = rmsnorm(h) * (next block's norm weight)."""
         nw = self._next_norm_weight(l)
+        if self.mode == "cats" and self.dense:
+            st = self._fn_dense(self.x2.data_ptr(), self.wg[l].data_ptr(), self.wu[l].data_ptr(),
+                                self.wd[l].data_ptr(), self.ws.ptr, self.ws.nbytes, self.B, self.H,
+                                self.I, self.code, self.thr[l], None, _lib.OUT_STORE, self.h.data_ptr(),
+                                self.x.data_ptr(), nw.data_ptr(), self.eps,
+                                torch.cuda.current_stream(self.dev).cuda_stream)
+            if st:
+                _lib.check(st, "cats_mlp_dense")
+            return
         if self.mode == "cats":
             st = self._fn(self.x2.data_ptr(), self.wg[l].data_ptr(), self.wu[l].data_ptr(),
                           self.wdt[l].data_ptr(), self.ws.ptr, self.ws.nbytes, self.B, self.H, self.I,

@@ -120,15 +120,29 @@ def flag_gemv_gemv_atomic(input, wgate, wup, wdown, output, threshold):
     ops.mlp(input, wgate, wup, wdown, _thr(threshold), out=output, accumulate_f32=True)
 
 
+def _dense_batch(input, wgate, wdown) -> bool:
+    """Batches take the dense tensor-core path where it is supported: these entry points receive
+    down_proj.weight as (H, I), which is what that path streams (and, like the reference's
+    stage 3 for these names, it reads all of it)."""
+    B, H = ops.batch_of(input)
+    return (ops.use_dense(B) and wdown.is_contiguous()
+            and ops.dense_supported(B, H, wgate.shape[0], input.dtype))
+
+
 def flag_gemv_gemv(input, wgate, wup, wdown, output, threshold):
     """Three-kernel pipeline writing ``output`` (same dtype as input); wdown is (H, I).
     Reference: flash_gemv.py:33-34, fuse_gemv_cmp_cuda.cu:2255-2328."""
+    if _dense_batch(input, wgate, wdown):
+        ops.mlp_dense(input, wgate, wup, wdown, _thr(threshold), out=output)
+        return
     ops.mlp(input, wgate, wup, ops.packed_wdt(wdown), _thr(threshold), out=output)
 
 
 def _inner(input, wgate, wup, wdown, threshold, dtype):
     if input.dtype != dtype:
         raise RuntimeError(f"flash_gemv: this entry point expects {dtype} tensors, got {input.dtype}")
+    if _dense_batch(input, wgate, wdown):
+        return ops.mlp_dense(input, wgate, wup, wdown, _thr(threshold))
     return ops.mlp(input, wgate, wup, ops.packed_wdt(wdown), _thr(threshold))
 
 

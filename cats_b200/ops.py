@@ -291,10 +291,28 @@ def mlp(x, wg, wu, wdt, threshold: float, out: Optional[torch.Tensor] = None,
     return out
 
 
-# Smallest batch that cats_b200 routes to the dense tensor-core path when the caller holds
-# down_proj.weight in its nn.Linear layout (module, decoder, flash_gemv's *_inner names).  With
-# independent masks at 50 % the union of four tokens' active sets is 94 % of the neurons.
-DENSE_MIN_BATCH = 3
+# Which path a batch takes when the caller holds down_proj.weight in both layouts.  The sparse
+# kernels stream all of Wg plus the union of the tokens' active rows of Wu and WdT, at about 0.55
+# of the HBM peak for batches of 2-4 (measured); the dense tensor-core path streams all three
+# matrices at about 0.75.  Equal time at a union density of about 0.6; beyond four tokens the
+# sparse path has no tensor-core kernel and the dense path always wins.
+DENSE_UNION_DENSITY = 0.6
+
+
+def use_dense(B: int, sparsity: Optional[float] = None, union_density: Optional[float] = None) -> bool:
+    """Density-aware switch between the sparse kernels and the dense tensor-core path.
+    ``union_density``: expected fraction of neurons active for at least one of the B tokens;
+    when unknown it is estimated from the per-token ``sparsity`` (default 0.5) as if the tokens'
+    masks were independent, 1 - sparsity**B (the reference tracks the measured quantity as
+    ``agg_sparsity``, experiments/models/sparse_silu/ugly_utils.py:594)."""
+    if B < 2:
+        return False
+    if B > 4:
+        return True
+    if union_density is None:
+        s = 0.5 if sparsity is None else min(max(float(sparsity), 0.0), 1.0)
+        union_density = 1.0 - s ** B
+    return union_density >= DENSE_UNION_DENSITY
 
 
 def dense_supported(B: int, H: int, I: int, dtype: torch.dtype) -> bool:

@@ -192,10 +192,22 @@ class CatsSparseSiluMLP(nn.Module):
                wd._version, id(self.wdown_t), torch.cuda.current_stream(x.device).cuda_stream
                if x.is_cuda else 0)
         if st is None or st[0] != key or not x.is_contiguous():
-            wdt = self.packed_down()
-            dev, dt, B, H, I = ops._check_mlp_weights(x, wg, wu, wdt)      # raises on misuse
+            B, H = ops.batch_of(x)
+            I = wg.shape[0]
+            # batches: density-aware switch to the dense tensor-core path, which reads
+            # down_proj.weight as it is (H, I); else the sparse kernels on the packed WdT (I, H)
+            if (ops.use_dense(B, self.__dict__.get("sparsity_level")) and x.is_cuda
+                    and wd.is_contiguous() and ops.dense_supported(B, H, I, x.dtype)):
+                ops._req(x, "input")
+                for w, name in ((wg, "gate weight"), (wu, "up weight"), (wd, "down weight")):
+                    ops._req(w, name, x.dtype, x.device)
+                fn, wdt, dev, dt = ops._lib.lib().cats_mlp_dense, wd, x.device, x.dtype
+            else:
+                wdt = self.packed_down()
+                dev, dt, B, H, I = ops._check_mlp_weights(x, wg, wu, wdt)      # raises on misuse
+                fn = ops._lib.lib().cats_mlp
             ws = ops.get_workspace(dev, H, I)
-            st = (key, ops._lib.lib().cats_mlp, wdt, ws, B, H, I, ops.dtype_code(dt), dev)
+            st = (key, fn, wdt, ws, B, H, I, ops.dtype_code(dt), dev)
             self.__dict__["_launch"] = st
         _, fn, wdt, ws, B, H, I, code, dev = st
         out = torch.empty_like(x)
@@ -358,6 +370,7 @@ def set_sparse_threshold(model, sparsity_level: float, use_relu: bool = False):
         else:
             mlp.dead_threshold = get_threshold(mlp.histogram_bins, mlp.post_act_hist_counts,
                                                sparsity_level)
+            mlp.sparsity_level = sparsity_level      # hint for the batch path switch
             mlp.sparse_act_fn.set_new_threshold(mlp.dead_threshold)
             mlp.regularization_threshold = mlp.dead_threshold * 1.2
 

@@ -22,7 +22,12 @@ from .synth import Layer
 
 
 class CatsMLPStack:
-    def __init__(self, layers: Sequence[Layer], batch: int = 1, eps: float = 1e-6):
+    """``dense``: None = decided by ``ops.use_dense(batch, sparsity)``; True / False force the
+    dense tensor-core path (one cooperative launch per layer, replayed from a CUDA graph) or the
+    sparse kernels."""
+
+    def __init__(self, layers: Sequence[Layer], batch: int = 1, eps: float = 1e-6,
+                 dense: Optional[bool] = None, sparsity: Optional[float] = None):
         if not layers:
             raise RuntimeError("cats_b200: empty layer stack")
         l0 = layers[0]
@@ -54,9 +59,47 @@ class CatsMLPStack:
         self.d2h_bytes = self.out_host.numel() * self.out_host.element_size()
         persistent = _lib.lib().cats_uses_persistent_kernel(self.L, batch, self.H, self.I, self.code)
         self.launches_per_step = 1 if persistent == 1 else 2 * self.L
+        want = ops.use_dense(batch, sparsity) if dense is None else bool(dense)
+        self.dense = want and ops.dense_supported(batch, self.H, self.I, self.dtype)
+        self.graph = None
+        if self.dense:
+            self._wd = [l.wd_contiguous() for l in self.layers]
+            self.launches_per_step = self.L
+
+    def _dense_layers(self) -> None:
+        cur, nxt = self.x, self.x_tmp
+        for l, wd in zip(self.layers, self._wd):
+            ops.mlp_dense(cur, l.wg, l.wu, wd, l.threshold, resid=self.resid, x_next=nxt,
+                          eps=self.eps, ws=self.ws)
+            cur, nxt = nxt, cur
+        if cur is not self.x:
+            self.x.copy_(cur)
+
+    def capture(self) -> None:
+        """Dense path: record the layers' launches into a CUDA graph (the state is restored)."""
+        if not self.dense or self.graph is not None:
+            return
+        keep = (self.x.clone(), self.resid.clone())
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._dense_layers()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._dense_layers()
+        self.graph = g
+        self.x.copy_(keep[0])
+        self.resid.copy_(keep[1])
 
     def run_device(self) -> None:
         """All layers on the state already in ``self.x`` / ``self.resid`` (device resident)."""
+        if self.dense:
+            if self.graph is None:
+                self.capture()
+            self.graph.replay()
+            return
         with ops._on(self.device):
             _lib.check(_lib.lib().cats_mlp_stack(
                 self.L, self._wg, self._wu, self._wdt, self._thr, self.x.data_ptr(),

@@ -40,6 +40,15 @@ class Layer:
         """down_proj.weight in nn.Linear layout (H, I) as a strided view (no copy)."""
         return self.wdt.t()
 
+    def wd_contiguous(self) -> torch.Tensor:
+        """down_proj.weight (H, I) as a contiguous tensor (made once, kept): what nn.Linear holds
+        and what the dense batched path streams."""
+        w = self.__dict__.get("_wd_hi")
+        if w is None:
+            w = self.wdt.t().contiguous()
+            self.__dict__["_wd_hi"] = w
+        return w
+
 
 def _gen(device, seed: int) -> torch.Generator:
     g = torch.Generator(device=device)

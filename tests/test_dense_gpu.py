@@ -118,3 +118,40 @@ def test_unsupported_shapes_are_refused(cuda_device):
     wd = torch.zeros((1024, 2752), device=cuda_device)
     with pytest.raises(RuntimeError, match="unsupported mode"):
         ops.mlp_dense(x, w, w, wd, 0.1)
+
+
+@pytest.mark.parametrize("B,dt", [(8, torch.float16), (3, torch.bfloat16)])
+def test_stack_on_the_dense_path_matches_the_oracle_chain(B, dt, cuda_device):
+    from cats_b200 import synth
+    from cats_b200.stack import CatsMLPStack
+
+    H, I, L = 4096, 14336, 2
+    layers = synth.make_stack(L, H, I, dt, cuda_device, 23, 0.5)
+    stack = CatsMLPStack(layers, batch=B)              # the switch picks the dense path here
+    assert stack.dense
+    bf16 = lambda a: torch.from_numpy(np.asarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+    rnd = np.float16 if dt == torch.float16 else bf16
+    for seed in (1, 2):                                  # graph replay with a new input
+        x0 = synth.make_x(B, H, dt, cuda_device, seed).reshape(B, H)
+        stack.set_input(x0)
+        stack.run_device()
+        torch.cuda.synchronize()
+        assert stack.ws.counters()[1] == 0
+        xe, re_, _ = O.mlp_stack(to_np(x0), [(to_np(l.wg), to_np(l.wu), to_np(l.wdt).T) for l in layers],
+                                 [l.threshold for l in layers], round_to=rnd)
+        tol = 2e-2 if dt == torch.float16 else 5e-2
+        assert O.rel_l2(to_np(stack.resid), re_) <= tol
+        assert O.rel_l2(to_np(stack.x), xe) <= tol
+
+
+
+
+@pytest.mark.gpu
+def test_the_switch_follows_batch_and_density():
+    from cats_b200 import ops
+
+    assert not ops.use_dense(1)
+    assert ops.use_dense(2) and ops.use_dense(4) and ops.use_dense(16)       # 50 %: union >= 0.75
+    assert not ops.use_dense(2, sparsity=0.7) and ops.use_dense(4, sparsity=0.7)
+    assert not ops.use_dense(4, sparsity=0.9) and ops.use_dense(8, sparsity=0.9)
+    assert not ops.use_dense(4, union_density=0.4) and ops.use_dense(3, union_density=0.9)

@@ -74,7 +74,7 @@ def test_stack_at_model_shape_twice_on_one_workspace(H, I, L, B, dt, sparsity, c
     layers = synth.make_stack(L, H, I, dt, cuda_device, 17, sparsity)
     assert _lib.lib().cats_uses_persistent_kernel(L, B, H, I, {torch.float32: 0, torch.float16: 1,
                                                                torch.bfloat16: 2}[dt]) == 1
-    stack = CatsMLPStack(layers, batch=B)
+    stack = CatsMLPStack(layers, batch=B, dense=False)     # the persistent sparse kernel
     np_layers = [(to_np(l.wg), to_np(l.wu), to_np(l.wdt).T) for l in layers]
     thr = [l.threshold for l in layers]
     for seed in (123, 456):
@@ -93,6 +93,8 @@ def test_stack_at_model_shape_twice_on_one_workspace(H, I, L, B, dt, sparsity, c
 
 @pytest.mark.parametrize("B", [8, 16])
 def test_large_batches_at_model_shape(B, cuda_device):
+    """The sparse kernels' own path for batches beyond four (direct loads): kept correct although
+    the dense tensor-core path (tests/test_dense_gpu.py) is the faster way at these sizes."""
     from test_parity_gpu import run_and_check, synth_case
 
     x, layer = synth_case(4096, 14336, B, torch.float16, 0.5, 40 + B, cuda_device)
