@@ -524,7 +524,7 @@ def measure_stack(name, H, I, dtype, L, s, B, args, D: Dist, regions, with_nccl=
     if D.world == 1 and stack.dense:
         # dense tensor-core path: every row of the three matrices is streamed
         streamed = 3 * esize * layers[0].wg.shape[0] * H + 4 * esize * B * H
-        block.update({"kernel": "k_dense_mlp (tcgen05, one cooperative launch per layer, CUDA graph)",
+        block.update({"kernel": "k_dense_stack (tcgen05, one cooperative launch for the stack)",
                       "bytes_streamed_per_layer": streamed,
                       "GBps_streamed": streamed / us_layer / 1e3,
                       "frac_of_peak_streamed": streamed / us_layer / 1e3 / peak,
@@ -767,6 +767,7 @@ def run_gpu_arm(args):
                                             parity_layers=min(3, L) if not args.no_parity else 0)
     ms_step, us_layer = head["ms_per_step"], head["us_per_layer"]
     dense_path = D.world == 1 and stack.dense
+    stack_launches = stack.launches_per_step
     I_local = head["intermediate_local"]
     persistent = head["kernel"] == "k_cats_mega"
 
@@ -816,7 +817,7 @@ def run_gpu_arm(args):
         }
     if D.world == 1 and stack.dense:
         streamed = head["bytes_streamed_per_layer"]
-        kname, launch_us, launch_bytes = "k_dense_mlp", us_layer, streamed
+        kname, launch_us, launch_bytes = "k_dense_stack", ms_step * 1e3, streamed * L
     elif persistent:
         kname, launch_us, launch_bytes = "k_cats_mega", ms_step * 1e3, bytes_layer * L
     elif staged:
@@ -834,8 +835,7 @@ def run_gpu_arm(args):
         "bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
         "bytes_per_launch": launch_bytes, "launch_us": launch_us,
-        "units_per_launch": ("1 layer" if (D.world == 1 and stack.dense) else
-                             f"{L} layers" if persistent else "1 layer stage"),
+        "units_per_launch": f"{L} layers" if (persistent or dense_path) else "1 layer stage",
         "frac_of_8TBps_nominal": achieved / 8000.0,
         "layer": {"bytes": bytes_layer, "us": us_layer, "GBps": bytes_layer / us_layer / 1e3,
                   "frac": bytes_layer / us_layer / 1e3 / peak,
@@ -920,7 +920,7 @@ def run_gpu_arm(args):
         res = time_cpu(H, I, L, s, B, args.seed, args.cpu_sample_layers, seconds=args.cpu_seconds)
         cpu = cpu_baseline_block(res, L, H, I, B)
 
-    launches = L if (D.world == 1 and dense_path) else 1 if persistent else 2 * L
+    launches = stack_launches if dense_path else 1 if persistent else 2 * L
     line = {
         "metric": METRIC, "value": B * 1e3 / ms_step, "unit": UNIT, "n_gpus": D.world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,

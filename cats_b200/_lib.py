@@ -51,6 +51,10 @@ SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_void_p,
                                 _c_void_p, _c_void_p, _c_float, _c_void_p]),
     "cats_dense_supported": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
+    "cats_mlp_stack_dense": (_c_int, [_c_int, ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
+                                      ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_float), _c_void_p,
+                                      _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
+                                      _c_int, _c_int, _c_float, _c_void_p]),
     "cats_mlp_static": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_void_p, _c_void_p]),
     "cats_mlp_static_limit": (_c_size_t, []),
@@ -78,6 +82,8 @@ SIGNATURES = {
                                  _c_void_p]),
     "cats_tail": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_int, _c_int,
                            _c_int, _c_void_p]),
+    "cats_rope_cache": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                 _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
     "cats_transpose": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]),
     "cats_read_counters": (_c_int, [_c_void_p, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int),
                                     _c_void_p]),

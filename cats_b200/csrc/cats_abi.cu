@@ -104,7 +104,6 @@ struct Options {
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
   int wait_ms = 1000;  // limit of every device-side wait (mbarrier, grid barrier, peer data)
-  int dense_fused = 1; // dense tensor-core path as one cooperative launch (0: two launches)
   int xchg = 0;        // tensor-parallel exchange: 0 = by the number of ranks, 1 = every CTA adds
                        // all ranks' partial sums, 2 = per-slice totals published by each CTA
 };
@@ -120,7 +119,6 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
     if (const char* e = getenv("CATS_B200_WAIT_MS")) v.wait_ms = atoi(e);
     if (const char* e = getenv("CATS_B200_XCHG")) v.xchg = atoi(e);
-    if (const char* e = getenv("CATS_B200_DENSE_FUSED")) v.dense_fused = atoi(e);
     return v;
   }();
   return o;
@@ -326,19 +324,11 @@ DensePlan plan_dense(int B, int H, int I, int dtype) {
   p.box_rows = (per_tile + 7) / 8 * 8;
   if (p.box_rows > 128) p.box_rows = 128;
   const size_t limit = (size_t)dev_info().max_smem_optin - 4096;   // static shared memory + slack
-  const size_t st1 = 2 * 16384 + 2048, st2 = 16384 + 2048;
-  p.S1 = (int)((limit - 1024) / st1);
-  p.S2 = (int)((limit - 1024) / st2);
-  if (p.S1 > 16) p.S1 = 16;
-  if (p.S2 > 16) p.S2 = 16;
-  if (p.S1 < 2 || p.S2 < 2) return p;
-  p.smem1 = p.S1 * st1 + 1024;
-  p.smem2 = p.S2 * st2 + 1024;
-  const size_t stf = 2 * 16384 + 4096;
+  const size_t stf = 2 * 16384 + 4096;                             // one 36 KB stage
   p.Sf = (int)((limit - 1024) / stf);
   if (p.Sf > 16) p.Sf = 16;
+  if (p.Sf < 2) return p;
   p.smemf = p.Sf * stf + 1024;
-  p.fused = (options().dense_fused && p.Sf >= 2 && p.grid <= dev_info().sms) ? 1 : 0;
   p.wait_kc = wait_kcycles();
   p.ok = true;
   return p;
@@ -413,7 +403,6 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "parts")) options().parts = value;
   else if (!strcmp(name, "wait_ms")) options().wait_ms = value;
   else if (!strcmp(name, "xchg")) options().xchg = value;
-  else if (!strcmp(name, "dense_fused")) options().dense_fused = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }
@@ -552,6 +541,34 @@ int cats_mlp_dense(const void* x, const void* Wg, const void* Wu, const void* Wd
   if (!dp.ok) return CATS_ERR_MODE;
   return cuda_status(inst_dense(dp, x, Wg, Wu, Wd, p, B, H, I, dtype, threshold, out, out_mode, resid,
                                 x_next, norm_weight, eps, static_cast<cudaStream_t>(stream)));
+}
+
+int cats_mlp_stack_dense(int L, const void* const* Wg, const void* const* Wu, const void* const* Wd,
+                         const float* thresholds, void* x_io, void* x_tmp, void* resid, void* ws,
+                         size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream) {
+  int s = check_common(B, H, I, dtype);
+  if (s) return s;
+  if (L < 1) return CATS_ERR_SHAPE;
+  if (!Wg || !Wu || !Wd || !thresholds || !x_io || !x_tmp || !resid) return CATS_ERR_NULL;
+  if (!aligned16(x_io) || !aligned16(x_tmp) || !aligned16(resid)) return CATS_ERR_ALIGN;
+  for (int l = 0; l < L; ++l) {
+    if (!Wg[l] || !Wu[l] || !Wd[l]) return CATS_ERR_NULL;
+    if (!aligned16(Wg[l]) || !aligned16(Wu[l]) || !aligned16(Wd[l])) return CATS_ERR_ALIGN;
+  }
+  WsPtrs p;
+  if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
+  const DensePlan dp = plan_dense(B, H, I, dtype);
+  if (!dp.ok) return CATS_ERR_MODE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // at most kDenseStackMaxLayers layers per launch; an odd-sized chunk leaves its result in x_io
+  // as well (the kernel's last layer always writes x_io), so chunks chain without copies
+  for (int l0 = 0; l0 < L; l0 += kDenseStackMaxLayers) {
+    const int n = (L - l0 < kDenseStackMaxLayers) ? L - l0 : kDenseStackMaxLayers;
+    cudaError_t e = inst_dense_stack(dp, n, Wg + l0, Wu + l0, Wd + l0, thresholds + l0, x_io, x_tmp,
+                                     resid, p, B, H, I, dtype, eps, st);
+    if (e != cudaSuccess) return cuda_status(e);
+  }
+  return CATS_OK;
 }
 
 int cats_dense_supported(int B, int H, int I, int dtype) {
@@ -790,6 +807,34 @@ int cats_tail(const void* y, void* resid, void* x_next, const void* norm_weight,
     e = launch(k_tail<__nv_bfloat16>, dim3(B), dim3(kThreads), 0, st, (const __nv_bfloat16*)y,
                (__nv_bfloat16*)resid, (__nv_bfloat16*)x_next, (const __nv_bfloat16*)norm_weight,
                eps, H);
+  return cuda_status(e);
+}
+
+int cats_rope_cache(const void* qkv, const void* cos_table, const void* sin_table,
+                    const long long* position, void* q_out, void* k_cache, void* v_cache, int B,
+                    int n_heads, int n_kv_heads, int head_dim, int max_len, int dtype, void* stream) {
+  if (dtype != CATS_F32 && dtype != CATS_F16 && dtype != CATS_BF16) return CATS_ERR_DTYPE;
+  if (B < 1 || n_heads < 1 || n_kv_heads < 1 || head_dim < 2 || head_dim % 2 || max_len < 1)
+    return CATS_ERR_SHAPE;
+  if (!qkv || !cos_table || !sin_table || !position || !q_out || !k_cache || !v_cache)
+    return CATS_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int warps = B * (n_heads + 2 * n_kv_heads);
+  const dim3 grid((warps + kWarps - 1) / kWarps), block(kThreads);
+  cudaError_t e;
+  if (dtype == CATS_F32)
+    e = launch(k_rope_cache<float>, grid, block, 0, st, (const float*)qkv, (const float*)cos_table,
+               (const float*)sin_table, position, (float*)q_out, (float*)k_cache, (float*)v_cache, B,
+               n_heads, n_kv_heads, head_dim, max_len);
+  else if (dtype == CATS_F16)
+    e = launch(k_rope_cache<__half>, grid, block, 0, st, (const __half*)qkv, (const __half*)cos_table,
+               (const __half*)sin_table, position, (__half*)q_out, (__half*)k_cache, (__half*)v_cache,
+               B, n_heads, n_kv_heads, head_dim, max_len);
+  else
+    e = launch(k_rope_cache<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)qkv,
+               (const __nv_bfloat16*)cos_table, (const __nv_bfloat16*)sin_table, position,
+               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, n_heads,
+               n_kv_heads, head_dim, max_len);
   return cuda_status(e);
 }
 

@@ -30,7 +30,9 @@ struct WsPtrs {
   float* seg_gate;   // [I * B]     gate value per list entry and token (0 = token inactive)
   int* flat_idx;     // [I]         globally ordered list (written by stage 2 / compact)
   float* h;          // [I * B]     gate * up per flat list entry and token
+  unsigned char* table;  // [kWsTableBytes] per-launch tables of the dense stack kernel (TMA maps)
 };
+constexpr size_t kWsTableBytes = 48 * 1024;
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -51,6 +53,7 @@ __host__ __device__ inline size_t ws_layout(void* base, int H, int I, WsPtrs* p)
   size_t o_sgate = take(sizeof(float) * (size_t)I * kMaxB);
   size_t o_fidx = take(sizeof(int) * (size_t)I);
   size_t o_h = take(sizeof(float) * (size_t)I * kMaxB);
+  size_t o_tab = take(kWsTableBytes);
   if (p) {
     p->hdr = reinterpret_cast<int*>(b + o_hdr);
     p->seg_count = reinterpret_cast<int*>(b + o_cnt);
@@ -59,6 +62,7 @@ __host__ __device__ inline size_t ws_layout(void* base, int H, int I, WsPtrs* p)
     p->seg_gate = reinterpret_cast<float*>(b + o_sgate);
     p->flat_idx = reinterpret_cast<int*>(b + o_fidx);
     p->h = reinterpret_cast<float*>(b + o_h);
+    p->table = reinterpret_cast<unsigned char*>(b + o_tab);
   }
   return off;
 }

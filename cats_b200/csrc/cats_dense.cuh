@@ -12,21 +12,8 @@
 // intermediate-major copy has no advantage, and [H, I] makes all three GEMMs the same shape of
 // problem - D[128 rows, tokens] += A[128 rows, K] * X[tokens, K]^T with both operands K-major.
 //
-//   k_dense_gateup   CTA c owns ~I/148 consecutive neurons.  Per 64-column step of the hidden
-//                    dimension one TMA box of Wg, one of Wu (box rows = the CTA's neurons, at
-//                    most 128) and one of x land in a shared-memory stage (128-byte swizzle);
-//                    one elected thread issues 2 x 4 tcgen05.mma (M 128, N 16, K 16) into two
-//                    TMEM accumulators; tcgen05.commit hands the stage back to the producer.
-//                    Epilogue (four warps, tcgen05.ld): h = mask(SiLU(g)) * u per token, rounded
-//                    to the storage type and written token-major [16, I] for the next kernel.
-//   k_dense_down     split-K: the (128-row tile of H) x (64-column step of I) blocks of Wd are
-//                    dealt out evenly over the CTAs in order; partial sums leave the TMEM
-//                    accumulator through fp32 reductions into the workspace accumulators, and
-//                    the CTA that finishes last runs the same fused tail as the sparse kernels
-//                    (store / residual add / RMS norm).  Its weight blocks do not depend on the
-//                    previous kernel, so they are in flight before griddepcontrol.wait.
-//
-// All waits are bounded (see cats_tma.cuh); a CTA that gives up frees its tensor memory first.
+// One cooperative kernel, k_dense, runs a layer or a whole stack of layers (see its comment).
+// All waits are bounded (cats_tma.cuh); a CTA that gives up frees its tensor memory first.
 // No cluster launch, no multicast: every TMA load is the plain single-CTA form.
 #pragma once
 
@@ -110,362 +97,85 @@ __host__ __device__ inline uint32_t umma_idesc(int fmt) {
   return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(kDenseN >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
 }
+// barrier among the four epilogue warps only (128 threads, named barrier 1)
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <typename T> struct UmmaFmt;
 template <> struct UmmaFmt<__half> { static constexpr int v = 0; };
 template <> struct UmmaFmt<__nv_bfloat16> { static constexpr int v = 1; };
 
 // ---------------------------------------------------------------------------------------------
-// gate + up: h[t, i] = mask_t(SiLU(Wg[i,:] . x[t,:])) * (Wu[i,:] . x[t,:])
-// Dynamic shared memory (after rounding its start up to 1024 bytes): S stages of
-// [Wg block 16 KB][Wu block 16 KB][x block 2 KB, padded to 1 KB multiples].
-// ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(kDenseThreads, 1)
-k_dense_gateup(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ CUtensorMap map_wu,
-               const __grid_constant__ CUtensorMap map_x, WsPtrs ws, int B, int H, int I, float thr,
-               T* __restrict__ h_out, int box_rows, int S, int wait_kc) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ int s_ctl[2];
-  int& s_abort = s_ctl[0];
-  __shared__ uint64_t s_bars[2 * 16 + 4];
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_count[4];
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int G = gridDim.x, c = blockIdx.x;
-  const int r0 = seg_row0(c, G, I), r1 = seg_row0(c + 1, G, I);
-  const int R = r1 - r0;
-  const int ntile = (R + box_rows - 1) / box_rows;         // row tiles of this CTA (1, or 2 at 70B)
-  const int rows_per_tile = ntile ? (R + ntile - 1) / ntile : 0;
-  const int nkb = (H + kDenseKB - 1) / kDenseKB;
-  const uint32_t stage_bytes = 2 * kDenseATile + 2048;     // x block padded to 2 KB
-  const uint32_t ring_u = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t full_u = smem_u32(s_bars), empty_u = full_u + 8u * S;
-  const uint32_t acc_full_u = empty_u + 8u * S, acc_empty_u = acc_full_u + 16u;
-  const uint32_t tx_bytes = 2u * (uint32_t)box_rows * 128u + kDenseXTile;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(full_u + 8u * s, 1);
-      mbar_init(empty_u + 8u * s, 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_u + 8u * b, 1);
-      mbar_init(acc_empty_u + 8u * b, 4);   // one arrival per epilogue warp
-    }
-    s_abort = 0;
-    s_ctl[1] = wait_kc;
-    mbar_fence_init();
-  }
-  if (tid < 4) s_count[tid] = 0;
-  if (warp == 1) tmem_alloc(smem_u32(&s_tmem), 64);   // 2 buffers x (gate 16 + up 16) columns
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = s_tmem;
-  pdl_launch_dependents();   // the next grid may become resident as soon as resources allow
-
-  if (warp == 0) {
-    // ================================================================== producer (one thread)
-    if (lane == 0) {
-      // weights never change: the first stages' weight blocks are in flight before the previous
-      // grid is done; their x blocks follow once x is final
-      const int total = ntile * nkb;
-      const int pre = total < S ? total : S;
-      for (int k = 0; k < pre; ++k) {
-        const int t = k / nkb, kb = k - t * nkb, row = r0 + t * rows_per_tile;
-        const uint32_t st = ring_u + (uint32_t)k * stage_bytes, bar = full_u + 8u * k;
-        mbar_expect_tx(bar, tx_bytes);
-        tma_load_2d(st, &map_wg, kb * kDenseKB, row, bar);
-        tma_load_2d(st + kDenseATile, &map_wu, kb * kDenseKB, row, bar);
-      }
-      pdl_wait();
-      fence_proxy_async_all();
-      for (int k = 0; k < pre; ++k)
-        tma_load_2d(ring_u + (uint32_t)k * stage_bytes + 2 * kDenseATile, &map_x, (k % nkb) * kDenseKB,
-                    0, full_u + 8u * k);
-      for (int k = pre; k < total; ++k) {
-        const int s = k % S;
-        if (!mbar_wait(empty_u + 8u * s, ((k / S) - 1) & 1, &s_abort)) break;
-        const int t = k / nkb, kb = k - t * nkb, row = r0 + t * rows_per_tile;
-        const uint32_t st = ring_u + (uint32_t)s * stage_bytes, bar = full_u + 8u * s;
-        mbar_expect_tx(bar, tx_bytes);
-        tma_load_2d(st, &map_wg, kb * kDenseKB, row, bar);
-        tma_load_2d(st + kDenseATile, &map_wu, kb * kDenseKB, row, bar);
-        tma_load_2d(st + 2 * kDenseATile, &map_x, kb * kDenseKB, 0, bar);
-      }
-    }
-  } else if (warp == 1) {
-    // ================================================================== MMA issuer (one thread)
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(UmmaFmt<T>::v);
-      int k = 0;
-      bool ok = true;
-      for (int t = 0; t < ntile && ok; ++t) {
-        const int buf = t & 1;
-        if (t >= 2) ok = mbar_wait(acc_empty_u + 8u * buf, ((t >> 1) - 1) & 1, &s_abort);
-        tc_fence_after();
-        const uint32_t tg = tmem_base + (uint32_t)buf * 32u, tu = tg + 16u;
-        for (int kb = 0; kb < nkb && ok; ++kb, ++k) {
-          const int s = k % S;
-          if (!(ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
-          tc_fence_after();
-          const uint32_t st = ring_u + (uint32_t)s * stage_bytes;
-          const uint64_t dg = umma_desc_k128(st), du = umma_desc_k128(st + kDenseATile),
-                         dx = umma_desc_k128(st + 2 * kDenseATile);
-#pragma unroll
-          for (int kk = 0; kk < kDenseKB / 16; ++kk) {
-            const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-            umma_f16(tg, dg + 2u * kk, dx + 2u * kk, idesc, acc);
-            umma_f16(tu, du + 2u * kk, dx + 2u * kk, idesc, acc);
-          }
-          umma_commit(empty_u + 8u * s);    // the stage is free once these MMAs have read it
-        }
-        if (ok) umma_commit(acc_full_u + 8u * buf);
-      }
-    }
-  } else {
-    // ================================================================== epilogue (4 warps)
-    const int q = warp & 3;                  // the TMEM lane quarter this warp may read
-    bool ok = true;
-    int my_count = 0;
-    for (int t = 0; t < ntile; ++t) {
-      const int buf = t & 1;
-      if (ok) ok = mbar_wait_warp(acc_full_u + 8u * buf, (t >> 1) & 1, &s_abort);
-      tc_fence_after();
-      if (ok) {
-        float g[16], u[16];
-        const uint32_t ta = tmem_base + (uint32_t)buf * 32u + ((uint32_t)(q * 32) << 16);
-        tmem_ld16(ta, g);
-        tmem_ld16(ta + 16u, u);
-        const int lr = t * rows_per_tile + q * 32 + lane;     // row within the CTA's range
-        const int tile_rows = min(rows_per_tile, R - t * rows_per_tile);
-        const bool valid = (q * 32 + lane) < tile_rows;
-        bool any = false;
-#pragma unroll
-        for (int tok = 0; tok < kDenseN; ++tok) {
-          if (tok < B) {
-            const float sv = silu_f(g[tok]);
-            const bool a = is_active(sv, thr);
-            any |= a;
-            if (valid) h_out[(size_t)tok * I + r0 + lr] = VecT<T>::from_f(a ? sv * u[tok] : 0.f);
-          }
-        }
-        my_count += __popc(__ballot_sync(0xffffffffu, valid && any));
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * buf);
-    }
-    if (lane == 0) s_count[q] = my_count;
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    ws.seg_count[c] = s_count[0] + s_count[1] + s_count[2] + s_count[3];
-    if (c == 0) ws.hdr[HDR_NSEG] = G;
-    if (s_abort) atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_DENSE);
-  }
-  if (s_abort) drain_after_abort();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 64);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// down: acc32[t, r] += sum over this CTA's blocks of Wd[r, i] * h[t, i]; last CTA: fused tail.
-// Blocks (128-row tile m of H, 64-column step kb of I) are numbered m * nkb + kb and CTA c takes
-// [c * U / G, (c + 1) * U / G): contiguous, so it touches few row tiles (two TMEM buffers alternate).
-// Stage: [Wd block 16 KB][h block 2 KB].
-// ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(kDenseThreads, 1)
-k_dense_down(const __grid_constant__ CUtensorMap map_wd, const __grid_constant__ CUtensorMap map_h,
-             WsPtrs ws, int B, int H, int I, T* __restrict__ out, int out_mode, T* __restrict__ resid,
-             T* __restrict__ x_next, const T* __restrict__ norm_w, float eps, int S, int wait_kc) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ int s_ctl[2];
-  int& s_abort = s_ctl[0];
-  __shared__ uint64_t s_bars[2 * 16 + 4];
-  __shared__ uint32_t s_tmem;
-  __shared__ float s_red[32];
-  __shared__ int s_last;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int G = gridDim.x, c = blockIdx.x;
-  const int nkb = (I + kDenseKB - 1) / kDenseKB, mt = H / 128;
-  const long long U = (long long)mt * nkb;
-  const int u0 = (int)((U * c) / G), u1 = (int)((U * (c + 1)) / G);
-  const int nu = u1 - u0;
-  const uint32_t stage_bytes = kDenseATile + 2048;
-  const uint32_t ring_u = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t full_u = smem_u32(s_bars), empty_u = full_u + 8u * S;
-  const uint32_t acc_full_u = empty_u + 8u * S, acc_empty_u = acc_full_u + 16u;
-  const uint32_t tx_bytes = kDenseATile + kDenseXTile;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(full_u + 8u * s, 1);
-      mbar_init(empty_u + 8u * s, 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_u + 8u * b, 1);
-      mbar_init(acc_empty_u + 8u * b, 4);
-    }
-    s_abort = 0;
-    s_ctl[1] = wait_kc;
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc(smem_u32(&s_tmem), 32);   // 2 buffers x 16 columns
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = s_tmem;
-  pdl_launch_dependents();
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // weight blocks first (they do not depend on the previous grid), then wait, then the h
-      // blocks of those stages; from then on both per stage
-      const int pre = nu < S ? nu : S;
-      for (int k = 0; k < pre; ++k) {
-        const int u = u0 + k, m = u / nkb, kb = u - m * nkb;
-        mbar_expect_tx(full_u + 8u * k, tx_bytes);
-        tma_load_2d(ring_u + (uint32_t)k * stage_bytes, &map_wd, kb * kDenseKB, m * 128, full_u + 8u * k);
-      }
-      pdl_wait();
-      fence_proxy_async_all();
-      for (int k = 0; k < pre; ++k) {
-        const int u = u0 + k, kb = u % nkb;
-        tma_load_2d(ring_u + (uint32_t)k * stage_bytes + kDenseATile, &map_h, kb * kDenseKB, 0,
-                    full_u + 8u * k);
-      }
-      for (int k = pre; k < nu; ++k) {
-        const int s = k % S;
-        if (!mbar_wait(empty_u + 8u * s, ((k / S) - 1) & 1, &s_abort)) break;
-        const int u = u0 + k, m = u / nkb, kb = u - m * nkb;
-        const uint32_t st = ring_u + (uint32_t)s * stage_bytes, bar = full_u + 8u * s;
-        mbar_expect_tx(bar, tx_bytes);
-        tma_load_2d(st, &map_wd, kb * kDenseKB, m * 128, bar);
-        tma_load_2d(st + kDenseATile, &map_h, kb * kDenseKB, 0, bar);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(UmmaFmt<T>::v);
-      bool ok = true;
-      int seg = 0, m_cur = -1;
-      bool first = true;
-      for (int k = 0; k < nu && ok; ++k) {
-        const int u = u0 + k, m = u / nkb;
-        if (m != m_cur) {
-          if (m_cur >= 0) {
-            umma_commit(acc_full_u + 8u * (seg & 1));
-            ++seg;
-          }
-          m_cur = m;
-          first = true;
-          if (seg >= 2) ok = mbar_wait(acc_empty_u + 8u * (seg & 1), ((seg >> 1) - 1) & 1, &s_abort);
-          tc_fence_after();
-          if (!ok) break;
-        }
-        const int s = k % S;
-        if (!(ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
-        tc_fence_after();
-        const uint32_t st = ring_u + (uint32_t)s * stage_bytes;
-        const uint64_t da = umma_desc_k128(st), dh = umma_desc_k128(st + kDenseATile);
-        const uint32_t td = tmem_base + (uint32_t)(seg & 1) * 16u;
-#pragma unroll
-        for (int kk = 0; kk < kDenseKB / 16; ++kk)
-          umma_f16(td, da + 2u * kk, dh + 2u * kk, idesc, (first && kk == 0) ? 0u : 1u);
-        first = false;
-        umma_commit(empty_u + 8u * s);
-      }
-      if (ok && m_cur >= 0) umma_commit(acc_full_u + 8u * (seg & 1));
-    }
-  } else {
-    const int q = warp & 3;
-    bool ok = true;
-    int seg = 0, m_cur = -1;
-    // walk the same block sequence to learn the row tiles this CTA touches
-    for (int k = 0; k <= nu; ++k) {
-      const int m = (k < nu) ? (u0 + k) / nkb : -2;
-      if (m == m_cur) continue;
-      if (m_cur >= 0) {
-        const int buf = seg & 1;
-        if (ok) ok = mbar_wait_warp(acc_full_u + 8u * buf, (seg >> 1) & 1, &s_abort);
-        tc_fence_after();
-        if (ok) {
-          float d[16];
-          tmem_ld16(tmem_base + (uint32_t)buf * 16u + ((uint32_t)(q * 32) << 16), d);
-          const int row = m_cur * 128 + q * 32 + lane;
-#pragma unroll
-          for (int tok = 0; tok < kDenseN; ++tok)
-            if (tok < B) atomicAdd(ws.acc32 + (size_t)tok * H + row, d[tok]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * buf);
-        ++seg;
-      }
-      m_cur = m;
-    }
-  }
-
-  // completion ticket: the CTA that arrives last owns the epilogue
-  __threadfence();
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    if (s_abort) atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_DENSE);
-    const unsigned t = atomicAdd(reinterpret_cast<unsigned*>(ws.hdr + HDR_TICKET), 1u);
-    s_last = (t == (unsigned)G - 1u) ? 1 : 0;
-  }
-  __syncthreads();
-  if (s_abort) drain_after_abort();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 32);
-  }
-  if (s_last) {
-    __threadfence();
-    finalize_down<T>(ws, B, H, out, out_mode, resid, x_next, norm_w, eps, s_red);
-    if (tid == 0) ws.hdr[HDR_TICKET] = 0;
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// The whole dense MLP in ONE cooperative launch: the two kernels above back to back in one ring.
+// k_dense: L dense CATS layers in ONE cooperative launch, one CTA per SM (the batched twin of
+// k_cats_mega).  Roles: warp 0 producer (one thread issues the TMA loads), warp 1 MMA issuer
+// (one thread), warps 2-5 epilogue (tcgen05.ld, activation, reductions, the tail).
 //
-// Why.  As separate launches each kernel pays its own ramp (first blocks in flight) and tail
-// (last CTA, single-CTA epilogue): measured at the Mistral shape, 73 us per layer for 352 MB.
-// Here one CTA per SM keeps one ring of 36 KB stages flowing through both GEMM phases:
-//   phase 1  stage = [Wg block][Wu block][x block]          -> h = mask(SiLU(g)) * u
-//   phase 2  stage = [Wd block][Wd block][h block][h block]  (two consecutive split-K blocks)
-// The Wd blocks do not depend on h, so the producer issues up to a ring's worth of them before it
-// waits for the grid barrier that says every CTA's h is written; only the small h blocks are
-// issued after it.  The tail is spread over all CTAs as well: after a second barrier (all partial
-// sums are in the fp32 accumulators) every CTA turns its own slice of the columns into out / the
-// new residual and adds its part of each token's sum of squares; after a third, it writes its
-// slice of the RMS-normalised x_next.
-// Grid barriers: one monotonic counter in the workspace header (four arrivals per CTA and
-// barrier, one per epilogue warp), its value at the start of the launch in the next slot; the
-// per-token sums of squares alternate between two header arrays by launch parity, the array the
-// next launch will use being cleared by this one.
+// Per layer a CTA streams two phases through one ring of 36 KB stages (128-byte swizzle):
+//   phase 1  stage = [Wg block][Wu block][x block]: the CTA owns ~I/148 consecutive neurons (one
+//            row tile of at most 128, two at the 70B shape); per 64-column step of H, 2 x 4
+//            tcgen05.mma (M 128, N 16, K 16) add into a gate and an up accumulator in TMEM;
+//            epilogue: h = mask(SiLU(g)) * u per token, rounded to the storage type, written
+//            token-major [16, I].
+//   phase 2  stage = [Wd block][Wd block][h block][h block]: split-K - the (128-row tile of H) x
+//            (64-column step of I) blocks of Wd [H, I] are dealt out evenly over the CTAs in
+//            order; partial sums leave TMEM through fp32 reductions into the workspace.
+//   tail     spread over all CTAs: every CTA turns its slice of the columns into out / the new
+//            residual and adds its part of each token's sum of squares, then writes its slice of
+//            x_next = rmsnorm(resid) (times the norm weight, if given).
+// Four grid barriers order a layer (one monotonic counter in the workspace header, four
+// arrivals per CTA and barrier - one per epilogue warp; its value at launch in the next slot):
+//   1 every CTA's h is written        2 every CTA's partial sums are added
+//   3 the sums of squares are complete  4 every CTA's slice of x_next is written
+// A stage's weight blocks never depend on a barrier, its activation block (x or h) does.  The
+// producer issues weight blocks as far ahead as the ring allows and keeps the stages whose
+// activation block is still owed in a FIFO: the block goes out as soon as its barrier has
+// completed (polled between stages) and at the latest when the ring wraps onto that stage.  So
+// the ring stays full across the h hand-off and across layers; only 2 KB per stage wait.
+// x alternates between two buffers from layer to layer; the last layer writes where the caller
+// asked (x_io for a stack).  The per-token sums of squares alternate between two header arrays,
+// the one the next layer (or launch) will use being cleared meanwhile.
+// The producer's and the issuer's bookkeeping is incremental on purpose: each is ONE thread that
+// has to handle a stage every ~0.7 us, and an integer division by a run-time value costs a tenth
+// of that (measured: 3.4 TB/s with a dozen divisions per stage, 6 TB/s without).
+// STACK: the layers' tensor maps and thresholds come from a table in global memory (written by
+// k_dense_table just before); else (one layer) from the kernel parameters.
 // ---------------------------------------------------------------------------------------------
 enum { HDR_DBAR = 16, HDR_DBAR_BASE = 17, HDR_DLAUNCH = 18, HDR_DSS = 32 /* [2][16] floats */ };
 constexpr uint32_t kDenseStage = 2 * kDenseATile + 4096;   // 36 KB, both phases
+constexpr int kDenseMaxLayers = 80;   // 80 x three 128-byte maps + thresholds in one 32 KB launch
+struct DenseLayerMaps {
+  CUtensorMap wg, wu, wd;
+};
+struct DenseStackParams {
+  DenseLayerMaps m[kDenseMaxLayers];
+  float thr[kDenseMaxLayers];
+};
+static_assert(sizeof(DenseStackParams) <= kWsTableBytes, "the table must fit its workspace region");
 
-template <typename T>
+// Copies the parameter block into the workspace table (one CTA; 16 bytes per thread and step).
+__global__ void __launch_bounds__(256)
+k_dense_table(const __grid_constant__ DenseStackParams P, DenseStackParams* dst) {
+  const uint4* src = reinterpret_cast<const uint4*>(&P);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  for (int i = threadIdx.x; i < (int)(sizeof(DenseStackParams) / 16); i += blockDim.x) d[i] = src[i];
+}
+
+// Outputs of the LAST layer (single-layer calls: the only one); earlier layers of a stack update
+// the residual in place and write x_next to the alternating buffer.
+struct DenseTail {
+  void* out;            // [B, H] raw MLP output (type T, or fp32 accumulate if out_mode == 1), or null
+  int out_mode;
+  void* resid;          // [B, H] residual stream in/out, or null
+  void* x_next;         // [B, H] rmsnorm(resid) [* norm_w], or null (needs resid)
+  const void* norm_w;   // [H] or null
+};
+
+template <typename T, bool STACK>
 __global__ void __launch_bounds__(kDenseThreads, 1)
-k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ CUtensorMap map_wu,
-            const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wd,
-            const __grid_constant__ CUtensorMap map_h, WsPtrs ws, int B, int H, int I, float thr,
-            T* __restrict__ h_buf, int box_rows, T* __restrict__ out, int out_mode,
-            T* __restrict__ resid, T* __restrict__ x_next, const T* __restrict__ norm_w, float eps,
-            int S, int wait_kc) {
+k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLayerMaps M1, float thr1,
+        const __grid_constant__ CUtensorMap map_xa, const __grid_constant__ CUtensorMap map_xb,
+        const __grid_constant__ CUtensorMap map_h, WsPtrs ws, int L, int B, int H, int I,
+        T* __restrict__ h_buf, int box_rows, T* __restrict__ x_tmp, const DenseTail tail, float eps,
+        int S, int wait_kc) {
   using V = VecT<T>;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int s_ctl[2];
@@ -473,6 +183,7 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
   __shared__ uint64_t s_bars[2 * 16 + 8];
   __shared__ uint32_t s_tmem;
   __shared__ int s_count[4];
+  __shared__ float s_ss[16];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, c = blockIdx.x;
@@ -482,13 +193,16 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
   const int ntile = (R + box_rows - 1) / box_rows;
   const int rows_per_tile = ntile ? (R + ntile - 1) / ntile : 0;
   const int nkb1 = (H + kDenseKB - 1) / kDenseKB;
-  const int n1 = ntile * nkb1;                              // phase-1 stages
+  const int n1 = ntile * nkb1;                              // phase-1 stages per layer
   // phase 2: this CTA's split-K blocks of Wd
   const int nkb2 = (I + kDenseKB - 1) / kDenseKB, mt = H / 128;
   const long long U = (long long)mt * nkb2;
   const int u0 = (int)((U * c) / G), u1 = (int)((U * (c + 1)) / G);
   const int nu = u1 - u0;
   const int n2 = (nu + 1) / 2;                              // phase-2 stages (two blocks each)
+  const int nl = n1 + n2;                                   // stages per layer
+  const int m_first = nu ? u0 / nkb2 : 0, m_last = nu ? (u1 - 1) / nkb2 : -1;
+  const int kb_first = nu ? u0 - m_first * nkb2 : 0;
 
   const uint32_t ring_u = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t full_u = smem_u32(s_bars), empty_u = full_u + 8u * S;
@@ -497,9 +211,10 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
 
   unsigned* dbar = reinterpret_cast<unsigned*>(ws.hdr + HDR_DBAR);
   const unsigned dbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_DBAR_BASE));
-  const int par = __ldcg(ws.hdr + HDR_DLAUNCH) & 1;
-  auto dtarget = [&](int n) { return dbase + (unsigned)n * 4u * (unsigned)G; };
-  const bool want_norm = resid != nullptr && x_next != nullptr && out_mode != 1;
+  const int par0 = __ldcg(ws.hdr + HDR_DLAUNCH) & 1;
+  // barrier n (1..4) of layer l
+  auto dtarget = [&](int l, int n) { return dbase + (unsigned)(4 * l + n) * 4u * (unsigned)G; };
+  auto maps = [&](int l) -> const DenseLayerMaps* { return STACK ? &Pg->m[l] : &M1; };
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -508,7 +223,7 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
     }
     for (int b = 0; b < 4; ++b) {           // 0,1: phase-1 accumulator pairs; 2,3: phase-2
       mbar_init(acc_full_u + 8u * b, 1);
-      mbar_init(acc_empty_u + 8u * b, 4);
+      mbar_init(acc_empty_u + 8u * b, 4);   // one arrival per epilogue warp
     }
     s_abort = 0;
     s_ctl[1] = wait_kc;
@@ -525,240 +240,297 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
     // ================================================================== producer (one thread)
     if (lane == 0) {
       bool ok = true;
-      int k = 0;
-      for (; k < n1 && ok; ++k) {
-        const int s = k % S;
-        if (k >= S && !(ok = mbar_wait(empty_u + 8u * s, ((k / S) - 1) & 1, &s_abort))) break;
-        const int t = k / nkb1, kb = k - t * nkb1, row = r0 + t * rows_per_tile;
-        const uint32_t st = ring_u + (uint32_t)s * kDenseStage, bar = full_u + 8u * s;
-        mbar_expect_tx(bar, tx1);
-        tma_load_2d(st, &map_wg, kb * kDenseKB, row, bar);
-        tma_load_2d(st + kDenseATile, &map_wu, kb * kDenseKB, row, bar);
-        tma_load_2d(st + 2 * kDenseATile, &map_x, kb * kDenseKB, 0, bar);
-      }
-      // phase 2: the weight blocks run ahead of the barrier by up to a ring
-      bool passed = false;
-      int pending0 = 0;   // first phase-2 stage whose h blocks are still to be issued
-      auto h_blocks = [&](int j) {
-        const int s = (n1 + j) % S, ua = u0 + 2 * j, nb = (2 * j + 1 < nu) ? 2 : 1;
-        const uint32_t st = ring_u + (uint32_t)s * kDenseStage + 2 * kDenseATile, bar = full_u + 8u * s;
-        for (int q = 0; q < nb; ++q)
-          tma_load_2d(st + (uint32_t)q * kDenseXTile, &map_h, ((ua + q) % nkb2) * kDenseKB, 0, bar);
+      const int total = L * nl;
+      // a cursor over the stages: layer l, stage r of the layer, ring slot s, ring cycle cy;
+      // phase 1: row tile t, column step kb; phase 2: first block's row tile m and column step kb
+      struct Cur { int k, l, r, s, cy, t, kb, m; };
+      auto advance = [&](Cur& q) {
+        ++q.k;
+        if (++q.s == S) { q.s = 0; ++q.cy; }
+        ++q.r;
+        if (q.r < n1) {
+          if (++q.kb == nkb1) { q.kb = 0; ++q.t; }
+        } else if (q.r == n1 && n2) {
+          q.m = m_first; q.kb = kb_first;                   // first phase-2 stage of the layer
+        } else if (q.r < nl) {
+          q.kb += 2;                                        // two blocks per stage
+          while (q.kb >= nkb2) { q.kb -= nkb2; ++q.m; }
+        } else {
+          q.r = 0; q.t = 0; q.kb = 0; ++q.l;
+          if (n1 == 0) { q.m = m_first; q.kb = kb_first; }
+        }
       };
-      auto pass = [&](int upto) {
-        if (!passed) {
-          ok = ok && grid_wait(dbar, dtarget(1), &s_abort);
-          fence_proxy_async_all();
-          passed = true;
-        }
-        if (ok)
-          for (; pending0 < upto; ++pending0) h_blocks(pending0);
+      // the barrier a stage's activation block waits for (0: none)
+      auto needs = [&](const Cur& q) {
+        if (q.r >= n1) return dtarget(q.l, 1);
+        return q.l ? dtarget(q.l - 1, 4) : 0u;
       };
-      for (int j = 0; j < n2 && ok; ++j, ++k) {
-        if (j == S) pass(j);                     // the ring wraps onto phase-2 stages: they need h
-        const int s = k % S;
-        if (k >= S && !(ok = mbar_wait(empty_u + 8u * s, ((k / S) - 1) & 1, &s_abort))) break;
-        const int ua = u0 + 2 * j, nb = (2 * j + 1 < nu) ? 2 : 1;
-        const uint32_t st = ring_u + (uint32_t)s * kDenseStage, bar = full_u + 8u * s;
-        mbar_expect_tx(bar, (uint32_t)nb * (kDenseATile + kDenseXTile));
-        for (int q = 0; q < nb; ++q) {
-          const int u = ua + q, m = u / nkb2, kb = u - m * nkb2;
-          tma_load_2d(st + (uint32_t)q * kDenseATile, &map_wd, kb * kDenseKB, m * 128, bar);
+      auto act_block = [&](const Cur& q) {
+        const uint32_t st = ring_u + (uint32_t)q.s * kDenseStage + 2 * kDenseATile, bar = full_u + 8u * q.s;
+        if (q.r < n1) {
+          tma_load_2d(st, (q.l & 1) ? &map_xb : &map_xa, q.kb * kDenseKB, 0, bar);
+        } else {
+          const int nb = (2 * (q.r - n1) + 1 < nu) ? 2 : 1;
+          int kb = q.kb;
+          for (int i = 0; i < nb; ++i) {
+            tma_load_2d(st + (uint32_t)i * kDenseXTile, &map_h, kb * kDenseKB, 0, bar);
+            if (++kb == nkb2) kb = 0;
+          }
         }
-        if (passed) {
-          h_blocks(j);
-          pending0 = j + 1;
+      };
+      Cur cur = {0, 0, 0, 0, 0, 0, 0, 0};     // next stage whose weight blocks go out
+      if (n1 == 0) { cur.m = m_first; cur.kb = kb_first; }
+      Cur pend = cur;                          // first stage whose activation block is still owed
+      unsigned done_target = dbase;            // highest barrier target known to have completed
+      // issue owed activation blocks of stages [pend, upto); `block`: wait for their barriers
+      auto settle = [&](int upto, bool block) {
+        while (pend.k < upto && ok) {
+          const unsigned need = needs(pend);
+          if (need && (int)(done_target - need) < 0) {
+            if (block) {
+              ok = grid_wait(dbar, need, &s_abort);
+              if (!ok) return;
+            } else if ((int)(ld_acquire_gpu(dbar) - need) < 0) {
+              return;
+            }
+            done_target = need;
+            fence_proxy_async_all();
+          }
+          act_block(pend);
+          advance(pend);
         }
+      };
+      while (cur.k < total && ok) {
+        if (cur.k >= S) {
+          settle(cur.k - S + 1, true);   // the stage this one replaces must be complete to drain
+          if (!ok) break;
+          if (!(ok = mbar_wait(empty_u + 8u * cur.s, (cur.cy - 1) & 1, &s_abort))) break;
+        }
+        const uint32_t st = ring_u + (uint32_t)cur.s * kDenseStage, bar = full_u + 8u * cur.s;
+        const DenseLayerMaps* mp = maps(cur.l);
+        if (cur.r < n1) {
+          const int row = r0 + cur.t * rows_per_tile;
+          mbar_expect_tx(bar, tx1);
+          tma_load_2d(st, &mp->wg, cur.kb * kDenseKB, row, bar);
+          tma_load_2d(st + kDenseATile, &mp->wu, cur.kb * kDenseKB, row, bar);
+        } else {
+          const int nb = (2 * (cur.r - n1) + 1 < nu) ? 2 : 1;
+          mbar_expect_tx(bar, (uint32_t)nb * (kDenseATile + kDenseXTile));
+          int m = cur.m, kb = cur.kb;
+          for (int i = 0; i < nb; ++i) {
+            tma_load_2d(st + (uint32_t)i * kDenseATile, &mp->wd, kb * kDenseKB, m * 128, bar);
+            if (++kb == nkb2) { kb = 0; ++m; }
+          }
+        }
+        advance(cur);
+        settle(cur.k, false);            // whatever is already allowed goes out now
       }
-      if (ok) pass(n2);
+      if (ok) settle(total, true);
     }
   } else if (warp == 1) {
     // ================================================================== MMA issuer (one thread)
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(UmmaFmt<T>::v);
-      int k = 0;
+      int tcount = 0, seg = 0, s = 0, cy = 0;   // ring slot and cycle, kept incrementally
       bool ok = true;
-      for (int t = 0; t < ntile && ok; ++t) {
-        const int buf = t & 1;
-        if (t >= 2) ok = mbar_wait(acc_empty_u + 8u * buf, ((t >> 1) - 1) & 1, &s_abort);
-        tc_fence_after();
-        const uint32_t tg = tmem_base + (uint32_t)buf * 32u, tu = tg + 16u;
-        for (int kb = 0; kb < nkb1 && ok; ++kb, ++k) {
-          const int s = k % S;
-          if (!(ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
+      for (int l = 0; l < L && ok; ++l) {
+        for (int t = 0; t < ntile && ok; ++t, ++tcount) {
+          const int buf = tcount & 1;
+          if (tcount >= 2) ok = mbar_wait(acc_empty_u + 8u * buf, ((tcount >> 1) - 1) & 1, &s_abort);
+          tc_fence_after();
+          const uint32_t tg = tmem_base + (uint32_t)buf * 32u, tu = tg + 16u;
+          for (int kb = 0; kb < nkb1 && ok; ++kb) {
+            if (!(ok = mbar_wait(full_u + 8u * s, cy & 1, &s_abort))) break;
+            tc_fence_after();
+            const uint32_t st = ring_u + (uint32_t)s * kDenseStage;
+            const uint64_t dg = umma_desc_k128(st), du = umma_desc_k128(st + kDenseATile),
+                           dx = umma_desc_k128(st + 2 * kDenseATile);
+#pragma unroll
+            for (int kk = 0; kk < kDenseKB / 16; ++kk) {
+              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+              umma_f16(tg, dg + 2u * kk, dx + 2u * kk, idesc, acc);
+              umma_f16(tu, du + 2u * kk, dx + 2u * kk, idesc, acc);
+            }
+            umma_commit(empty_u + 8u * s);    // the stage is free once these MMAs have read it
+            if (++s == S) { s = 0; ++cy; }
+          }
+          if (ok) umma_commit(acc_full_u + 8u * buf);
+        }
+        int m_cur = -1, m2 = m_first, kb2 = kb_first;
+        bool first = true;
+        for (int j = 0; j < n2 && ok; ++j) {
+          if (!(ok = mbar_wait(full_u + 8u * s, cy & 1, &s_abort))) break;
           tc_fence_after();
           const uint32_t st = ring_u + (uint32_t)s * kDenseStage;
-          const uint64_t dg = umma_desc_k128(st), du = umma_desc_k128(st + kDenseATile),
-                         dx = umma_desc_k128(st + 2 * kDenseATile);
-#pragma unroll
-          for (int kk = 0; kk < kDenseKB / 16; ++kk) {
-            const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-            umma_f16(tg, dg + 2u * kk, dx + 2u * kk, idesc, acc);
-            umma_f16(tu, du + 2u * kk, dx + 2u * kk, idesc, acc);
-          }
-          umma_commit(empty_u + 8u * s);
-        }
-        if (ok) umma_commit(acc_full_u + 8u * buf);
-      }
-      // phase 2
-      int seg = 0, m_cur = -1;
-      bool first = true;
-      for (int j = 0; j < n2 && ok; ++j, ++k) {
-        const int s = k % S;
-        if (!(ok = mbar_wait(full_u + 8u * s, (k / S) & 1, &s_abort))) break;
-        tc_fence_after();
-        const uint32_t st = ring_u + (uint32_t)s * kDenseStage;
-        const int nb = (2 * j + 1 < nu) ? 2 : 1;
-        for (int q = 0; q < nb && ok; ++q) {
-          const int m = (u0 + 2 * j + q) / nkb2;
-          if (m != m_cur) {
-            if (m_cur >= 0) {
-              umma_commit(acc_full_u + 8u * (2 + (seg & 1)));
-              ++seg;
+          const int nb = (2 * j + 1 < nu) ? 2 : 1;
+          for (int q = 0; q < nb && ok; ++q) {
+            const int m = m2;
+            if (++kb2 == nkb2) { kb2 = 0; ++m2; }
+            if (m != m_cur) {
+              if (m_cur >= 0) {
+                umma_commit(acc_full_u + 8u * (2 + (seg & 1)));
+                ++seg;
+              }
+              m_cur = m;
+              first = true;
+              if (seg >= 2)
+                ok = mbar_wait(acc_empty_u + 8u * (2 + (seg & 1)), ((seg >> 1) - 1) & 1, &s_abort);
+              tc_fence_after();
+              if (!ok) break;
             }
-            m_cur = m;
-            first = true;
-            if (seg >= 2)
-              ok = mbar_wait(acc_empty_u + 8u * (2 + (seg & 1)), ((seg >> 1) - 1) & 1, &s_abort);
-            tc_fence_after();
-            if (!ok) break;
-          }
-          const uint64_t da = umma_desc_k128(st + (uint32_t)q * kDenseATile),
-                         dh = umma_desc_k128(st + 2 * kDenseATile + (uint32_t)q * kDenseXTile);
-          const uint32_t td = tmem_base + 64u + (uint32_t)(seg & 1) * 16u;
+            const uint64_t da = umma_desc_k128(st + (uint32_t)q * kDenseATile),
+                           dh = umma_desc_k128(st + 2 * kDenseATile + (uint32_t)q * kDenseXTile);
+            const uint32_t td = tmem_base + 64u + (uint32_t)(seg & 1) * 16u;
 #pragma unroll
-          for (int kk = 0; kk < kDenseKB / 16; ++kk)
-            umma_f16(td, da + 2u * kk, dh + 2u * kk, idesc, (first && kk == 0) ? 0u : 1u);
-          first = false;
+            for (int kk = 0; kk < kDenseKB / 16; ++kk)
+              umma_f16(td, da + 2u * kk, dh + 2u * kk, idesc, (first && kk == 0) ? 0u : 1u);
+            first = false;
+          }
+          if (ok) umma_commit(empty_u + 8u * s);
+          if (++s == S) { s = 0; ++cy; }
         }
-        if (ok) umma_commit(empty_u + 8u * s);
+        if (ok && m_cur >= 0) {
+          umma_commit(acc_full_u + 8u * (2 + (seg & 1)));
+          ++seg;
+        }
       }
-      if (ok && m_cur >= 0) umma_commit(acc_full_u + 8u * (2 + (seg & 1)));
     }
   } else {
     // ================================================================== epilogue (4 warps)
-    const int q = warp & 3;
+    const int q = warp & 3;                  // the TMEM lane quarter this warp may read
     const int et = q * 32 + lane;            // 0..127 among the epilogue threads
     bool ok = true;
-    int my_count = 0;
-    // ---- phase 1: h = mask(SiLU(g)) * u
-    for (int t = 0; t < ntile; ++t) {
-      const int buf = t & 1;
-      if (ok) ok = mbar_wait_warp(acc_full_u + 8u * buf, (t >> 1) & 1, &s_abort);
-      tc_fence_after();
-      if (ok) {
-        float g[16], u[16];
-        const uint32_t ta = tmem_base + (uint32_t)buf * 32u + ((uint32_t)(q * 32) << 16);
-        tmem_ld16(ta, g);
-        tmem_ld16(ta + 16u, u);
-        const int lr = t * rows_per_tile + q * 32 + lane;
-        const int tile_rows = min(rows_per_tile, R - t * rows_per_tile);
-        const bool valid = (q * 32 + lane) < tile_rows;
-        bool any = false;
-#pragma unroll
-        for (int tok = 0; tok < kDenseN; ++tok) {
-          if (tok < B) {
-            const float sv = silu_f(g[tok]);
-            const bool a = is_active(sv, thr);
-            any |= a;
-            if (valid) h_buf[(size_t)tok * I + r0 + lr] = V::from_f(a ? sv * u[tok] : 0.f);
-          }
-        }
-        my_count += __popc(__ballot_sync(0xffffffffu, valid && any));
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * buf);
-    }
-    if (lane == 0) s_count[q] = my_count;
-    __syncwarp();
-    if (lane == 0 && ok) grid_arrive(dbar);          // barrier 1: this warp's h rows are written
-    // ---- phase 2: partial sums into the fp32 accumulators
-    {
-      int seg = 0, m_cur = -1;
-      for (int k = 0; k <= nu; ++k) {
-        const int m = (k < nu) ? (u0 + k) / nkb2 : -2;
-        if (m == m_cur) continue;
-        if (m_cur >= 0) {
-          const int buf = seg & 1;
-          if (ok) ok = mbar_wait_warp(acc_full_u + 8u * (2 + buf), (seg >> 1) & 1, &s_abort);
-          tc_fence_after();
-          if (ok) {
-            float d[16];
-            tmem_ld16(tmem_base + 64u + (uint32_t)buf * 16u + ((uint32_t)(q * 32) << 16), d);
-            const int row = m_cur * 128 + q * 32 + lane;
-#pragma unroll
-            for (int tok = 0; tok < kDenseN; ++tok)
-              if (tok < B) atomicAdd(ws.acc32 + (size_t)tok * H + row, d[tok]);
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * (2 + buf));
-          ++seg;
-        }
-        m_cur = m;
-      }
-    }
-    __syncwarp();
-    if (lane == 0 && ok) grid_arrive(dbar);          // barrier 2: this warp's sums are added
-    if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(2), &s_abort);   // one polling lane per warp
-    ok = __all_sync(0xffffffffu, ok);
-    // ---- tail, this CTA's slice of the columns (groups of four), all tokens
+    int my_count = 0, tcount = 0, seg = 0;
     const int ngrp = H >> 2;
     const int own_lo = (int)(((long long)ngrp * c) / G), own_hi = (int)(((long long)ngrp * (c + 1)) / G);
     const int own_n = own_hi - own_lo;
-    float* ss_cur = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + par * 16;
-    float* ss_nxt = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + (par ^ 1) * 16;
-    if (c == 0 && et < 16) ss_nxt[et] = 0.f;         // for the next launch on this workspace
-    for (int e = et; e < B * own_n && ok; e += 128) {
-      const int b = e / own_n, g = own_lo + (e - b * own_n);
-      float4* ap = reinterpret_cast<float4*>(ws.acc32 + (size_t)b * H) + g;
-      const float4 a = __ldcg(ap);
-      *ap = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float v[4] = {a.x, a.y, a.z, a.w};
-      const size_t o = (size_t)b * H + 4 * (size_t)g;
-      if (out_mode == 1) {
-        float* of = reinterpret_cast<float*>(out) + o;
+    T* x_io = reinterpret_cast<T*>(tail.x_next);   // (stacks: the caller passes x_io here)
+    for (int l = 0; l < L; ++l) {
+      const bool last = l + 1 == L;
+      const float thr = STACK ? __ldg(&Pg->thr[l]) : thr1;
+      my_count = 0;
+      // ---- phase 1: h = mask(SiLU(g)) * u
+      for (int t = 0; t < ntile; ++t, ++tcount) {
+        const int buf = tcount & 1;
+        if (ok) ok = mbar_wait_warp(acc_full_u + 8u * buf, (tcount >> 1) & 1, &s_abort);
+        tc_fence_after();
+        if (ok) {
+          float g[16], u[16];
+          const uint32_t ta = tmem_base + (uint32_t)buf * 32u + ((uint32_t)(q * 32) << 16);
+          tmem_ld16(ta, g);
+          tmem_ld16(ta + 16u, u);
+          const int lr = t * rows_per_tile + q * 32 + lane;     // row within the CTA's range
+          const int tile_rows = min(rows_per_tile, R - t * rows_per_tile);
+          const bool valid = (q * 32 + lane) < tile_rows;
+          bool any = false;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) of[i] += v[i];
-      } else {
-        if (out) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) out[o + i] = V::from_f(v[i]);
-        }
-        if (resid) {
-          float ssq = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const T rn = V::from_f(V::to_f(resid[o + i]) + v[i]);
-            resid[o + i] = rn;
-            const float rf = V::to_f(rn);
-            ssq = fmaf(rf, rf, ssq);
+          for (int tok = 0; tok < kDenseN; ++tok) {
+            if (tok < B) {
+              const float sv = silu_f(g[tok]);
+              const bool a = is_active(sv, thr);
+              any |= a;
+              if (valid) h_buf[(size_t)tok * I + r0 + lr] = V::from_f(a ? sv * u[tok] : 0.f);
+            }
           }
-          if (want_norm) atomicAdd(ss_cur + b, ssq);
+          my_count += __popc(__ballot_sync(0xffffffffu, valid && any));
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * buf);
       }
-    }
-    if (want_norm) {
       __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);        // barrier 3: the sums of squares are complete
-      if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(3), &s_abort);
+      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 1
+      // ---- phase 2: partial sums into the fp32 accumulators, one row tile at a time
+      for (int m_cur = m_first; m_cur <= m_last; ++m_cur, ++seg) {
+        const int buf = seg & 1;
+        if (ok) ok = mbar_wait_warp(acc_full_u + 8u * (2 + buf), (seg >> 1) & 1, &s_abort);
+        tc_fence_after();
+        if (ok) {
+          float d[16];
+          tmem_ld16(tmem_base + 64u + (uint32_t)buf * 16u + ((uint32_t)(q * 32) << 16), d);
+          const int row = m_cur * 128 + q * 32 + lane;
+#pragma unroll
+          for (int tok = 0; tok < kDenseN; ++tok)
+            if (tok < B) atomicAdd(ws.acc32 + (size_t)tok * H + row, d[tok]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * (2 + buf));
+      }
+      __syncwarp();
+      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 2
+      if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(l, 2), &s_abort);        // one poller per warp
       ok = __all_sync(0xffffffffu, ok);
+      // ---- tail, this CTA's slice of the columns (groups of four), all tokens
+      T* out = last ? reinterpret_cast<T*>(tail.out) : nullptr;
+      const int out_mode = last ? tail.out_mode : 0;
+      T* resid = reinterpret_cast<T*>(tail.resid);
+      // x_{l+1}: the alternating buffers inside a stack, the caller's pointer after the last layer
+      T* xn = last ? reinterpret_cast<T*>(tail.x_next) : ((l & 1) ? x_io : x_tmp);
+      const T* norm_w = last ? reinterpret_cast<const T*>(tail.norm_w) : nullptr;
+      const bool want_norm = resid != nullptr && xn != nullptr && out_mode != 1;
+      const int par = (par0 + l) & 1;
+      float* ss_cur = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + par * 16;
+      float* ss_nxt = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + (par ^ 1) * 16;
+      if (c == 0 && et < 16) ss_nxt[et] = 0.f;         // for the next layer / launch
+      if (et < 16) s_ss[et] = 0.f;
+      epilogue_bar_sync();
       for (int e = et; e < B * own_n && ok; e += 128) {
         const int b = e / own_n, g = own_lo + (e - b * own_n);
-        const float rsq = rsqrtf(__ldcg(ss_cur + b) / (float)H + eps);
+        float4* ap = reinterpret_cast<float4*>(ws.acc32 + (size_t)b * H) + g;
+        const float4 a = __ldcg(ap);
+        *ap = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float v[4] = {a.x, a.y, a.z, a.w};
         const size_t o = (size_t)b * H + 4 * (size_t)g;
+        if (out_mode == 1) {
+          float* of = reinterpret_cast<float*>(out) + o;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          T y = V::from_f(V::to_f(resid[o + i]) * rsq);
-          if (norm_w) y = V::from_f(V::to_f(norm_w[4 * g + i]) * V::to_f(y));
-          x_next[o + i] = y;
+          for (int i = 0; i < 4; ++i) of[i] += v[i];
+        } else {
+          if (out) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[o + i] = V::from_f(v[i]);
+          }
+          if (resid) {
+            float ssq = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const T rn = V::from_f(V::to_f(resid[o + i]) + v[i]);
+              resid[o + i] = rn;
+              const float rf = V::to_f(rn);
+              ssq = fmaf(rf, rf, ssq);
+            }
+            if (want_norm) atomicAdd(&s_ss[b], ssq);   // per CTA in shared memory first
+          }
         }
       }
-    } else {
+      if (want_norm) {
+        // one global add per CTA and token: thousands of adds to the same few addresses would
+        // serialise in L2
+        epilogue_bar_sync();
+        if (et < B && ok) atomicAdd(ss_cur + et, s_ss[et]);
+      }
       __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);        // keeps three rounds of arrivals per launch
+      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 3
+      if (want_norm) {
+        if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(l, 3), &s_abort);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int e = et; e < B * own_n && ok; e += 128) {
+          const int b = e / own_n, g = own_lo + (e - b * own_n);
+          const float rsq = rsqrtf(__ldcg(ss_cur + b) / (float)H + eps);
+          const size_t o = (size_t)b * H + 4 * (size_t)g;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            T y = V::from_f(V::to_f(resid[o + i]) * rsq);
+            if (norm_w) y = V::from_f(V::to_f(norm_w[4 * g + i]) * V::to_f(y));
+            xn[o + i] = y;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 4
     }
+    if (lane == 0) s_count[q] = my_count;
   }
 
   tc_fence_before();
@@ -769,8 +541,8 @@ k_dense_mlp(const __grid_constant__ CUtensorMap map_wg, const __grid_constant__ 
       atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_DENSE);
     } else if (c == 0) {
       ws.hdr[HDR_NSEG] = G;
-      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + 12u * (unsigned)G);
-      ws.hdr[HDR_DLAUNCH] = par ^ 1;
+      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + (unsigned)(16 * L) * (unsigned)G);
+      ws.hdr[HDR_DLAUNCH] = (par0 + L) & 1;
     }
   }
   if (s_abort) drain_after_abort();

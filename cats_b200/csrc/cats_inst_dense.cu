@@ -77,46 +77,84 @@ bool tensor_map(const void* ptr, int rows, int cols, int box_rows, int dtype, CU
   return true;
 }
 
+template <typename T, bool STACK, typename... Args>
+cudaError_t launch_coop(const DensePlan& p, cudaStream_t st, Args... args) {
+  // cooperative: the CTAs wait for one another at grid barriers
+  auto kernel = k_dense<T, STACK>;
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smemf);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(p.grid);
+  cfg.blockDim = dim3(kDenseThreads);
+  cfg.dynamicSmemBytes = p.smemf;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename T>
 cudaError_t launch_dense(const DensePlan& p, const void* x, const void* Wg, const void* Wu,
                          const void* Wd, WsPtrs ws, int B, int H, int I, int dtype, float thr, void* out,
                          int out_mode, void* resid, void* x_next, const void* norm_w, float eps,
                          cudaStream_t st) {
-  CUtensorMap m_wg, m_wu, m_x, m_wd, m_h;
+  DenseLayerMaps M;
+  CUtensorMap m_x, m_h;
   T* h = reinterpret_cast<T*>(ws.h);   // [16, I] of T: the list array is not used on this path
-  if (!tensor_map(Wg, I, H, p.box_rows, dtype, &m_wg) || !tensor_map(Wu, I, H, p.box_rows, dtype, &m_wu) ||
-      !tensor_map(x, B, H, kDenseN, dtype, &m_x) || !tensor_map(Wd, H, I, 128, dtype, &m_wd) ||
+  if (!tensor_map(Wg, I, H, p.box_rows, dtype, &M.wg) || !tensor_map(Wu, I, H, p.box_rows, dtype, &M.wu) ||
+      !tensor_map(x, B, H, kDenseN, dtype, &m_x) || !tensor_map(Wd, H, I, 128, dtype, &M.wd) ||
       !tensor_map(h, B, I, kDenseN, dtype, &m_h))
     return cudaErrorInvalidValue;
-  if (p.fused) {
-    // one cooperative launch: the CTAs wait for one another at grid barriers
-    auto kernel = k_dense_mlp<T>;
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smemf);
-    if (e != cudaSuccess) return e;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3(kDenseThreads);
-    cfg.dynamicSmemBytes = p.smemf;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, m_wg, m_wu, m_x, m_wd, m_h, ws, B, H, I, thr, h, p.box_rows,
-                              (T*)out, out_mode, (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.Sf,
-                              p.wait_kc);
+  const DenseTail tail{out, out_mode, resid, x_next, norm_w};
+  return launch_coop<T, false>(p, st, (const DenseStackParams*)nullptr, M, thr, m_x, m_x, m_h, ws, 1, B, H,
+                               I, h, p.box_rows, (T*)nullptr, tail, eps, p.Sf, p.wait_kc);
+}
+
+template <typename T>
+cudaError_t launch_dense_stack(const DensePlan& p, int L, const void* const* Wg, const void* const* Wu,
+                               const void* const* Wd, const float* thr, void* x_io, void* x_tmp,
+                               void* resid, WsPtrs ws, int B, int H, int I, int dtype, float eps,
+                               cudaStream_t st) {
+  static thread_local DenseStackParams P;   // ~31 KB: off the stack; filled per call
+  CUtensorMap m_xa, m_xb, m_h;
+  T* h = reinterpret_cast<T*>(ws.h);
+  for (int l = 0; l < L; ++l) {
+    if (!tensor_map(Wg[l], I, H, p.box_rows, dtype, &P.m[l].wg) ||
+        !tensor_map(Wu[l], I, H, p.box_rows, dtype, &P.m[l].wu) ||
+        !tensor_map(Wd[l], H, I, 128, dtype, &P.m[l].wd))
+      return cudaErrorInvalidValue;
+    P.thr[l] = thr[l];
   }
-  cudaError_t e = launch(k_dense_gateup<T>, dim3(p.grid), dim3(kDenseThreads), p.smem1, st, m_wg, m_wu, m_x,
-                         ws, B, H, I, thr, h, p.box_rows, p.S1, p.wait_kc);
+  if (!tensor_map(x_io, B, H, kDenseN, dtype, &m_xa) || !tensor_map(x_tmp, B, H, kDenseN, dtype, &m_xb) ||
+      !tensor_map(h, B, I, kDenseN, dtype, &m_h))
+    return cudaErrorInvalidValue;
+  // the table goes to global memory first (a launch, so the call stays capturable in a graph)
+  DenseStackParams* table = reinterpret_cast<DenseStackParams*>(ws.table);
+  k_dense_table<<<1, 256, 0, st>>>(P, table);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  return launch(k_dense_down<T>, dim3(p.grid), dim3(kDenseThreads), p.smem2, st, m_wd, m_h, ws, B, H, I,
-                (T*)out, out_mode, (T*)resid, (T*)x_next, (const T*)norm_w, eps, p.S2, p.wait_kc);
+  const DenseTail tail{nullptr, 0, resid, x_io, nullptr};   // the last layer writes x_io
+  return launch_coop<T, true>(p, st, (const DenseStackParams*)table, P.m[0], 0.f, m_xa, m_xb, m_h, ws, L, B,
+                              H, I, h, p.box_rows, (T*)x_tmp, tail, eps, p.Sf, p.wait_kc);
 }
 
 }  // namespace
+
+cudaError_t inst_dense_stack(const DensePlan& p, int L, const void* const* Wg, const void* const* Wu,
+                             const void* const* Wd, const float* thr, void* x_io, void* x_tmp,
+                             void* resid, WsPtrs ws, int B, int H, int I, int dtype, float eps,
+                             cudaStream_t st) {
+  if (L < 1 || L > kDenseMaxLayers) return cudaErrorInvalidValue;
+  if (dtype == 1)
+    return launch_dense_stack<__half>(p, L, Wg, Wu, Wd, thr, x_io, x_tmp, resid, ws, B, H, I, dtype, eps, st);
+  return launch_dense_stack<__nv_bfloat16>(p, L, Wg, Wu, Wd, thr, x_io, x_tmp, resid, ws, B, H, I, dtype,
+                                           eps, st);
+}
 
 cudaError_t inst_dense(const DensePlan& p, const void* x, const void* Wg, const void* Wu, const void* Wd,
                        WsPtrs ws, int B, int H, int I, int dtype, float thr, void* out, int out_mode,

@@ -592,4 +592,50 @@ __global__ void k_transpose(const E* __restrict__ src, E* __restrict__ dst, int 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode-step glue between the fused QKV projection and attention: rotate-half RoPE on the query
+// and key heads of ONE new position per sequence, and the write of the rotated keys and the
+// values into the static KV cache at that position - what HF's apply_rotary_pos_emb plus the
+// cache update do in a dozen elementwise launches.  Arithmetic in the storage type with a rounding
+// after every operation (q * cos, rotate_half(q) * sin, their sum), as those launches round.
+//   qkv   [B, (nh + 2 * nkv) * hd]   q heads, then k heads, then v heads
+//   cos, sin [max_len, hd] (the two halves of a row are equal); *pos = the position
+//   q_out [B, nh, hd];  kc, vc [B, nkv, max_len, hd]
+// One warp per (sequence, head); hd a multiple of 64, at most 256.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+k_rope_cache(const T* __restrict__ qkv, const T* __restrict__ cosv, const T* __restrict__ sinv,
+             const long long* __restrict__ pos_ptr, T* __restrict__ q_out, T* __restrict__ kc,
+             T* __restrict__ vc, int B, int nh, int nkv, int hd, int max_len) {
+  using V = VecT<T>;
+  const int warp = (blockIdx.x * kThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int heads = nh + 2 * nkv;
+  if (warp >= B * heads) return;
+  const int b = warp / heads, h = warp - b * heads;
+  const long long pos = *pos_ptr;
+  if (pos < 0 || pos >= max_len) return;
+  const T* src = qkv + ((size_t)b * heads + h) * hd;
+  const int half = hd >> 1;
+  if (h >= nh + nkv) {                                   // value head: copy
+    T* dst = vc + (((size_t)b * nkv + (h - nh - nkv)) * max_len + pos) * hd;
+    for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+    return;
+  }
+  T* dst = (h < nh) ? q_out + ((size_t)b * nh + h) * hd
+                    : kc + (((size_t)b * nkv + (h - nh)) * max_len + pos) * hd;
+  const T* c = cosv + (size_t)pos * hd;
+  const T* s = sinv + (size_t)pos * hd;
+  for (int i = lane; i < half; i += 32) {
+    const float x1 = V::to_f(src[i]), x2 = V::to_f(src[i + half]);
+    // rounded to T after each operation, as the separate launches of the eager path round
+    const float a1 = V::to_f(V::from_f(x1 * V::to_f(c[i])));
+    const float b1 = V::to_f(V::from_f(-x2 * V::to_f(s[i])));
+    const float a2 = V::to_f(V::from_f(x2 * V::to_f(c[i + half])));
+    const float b2 = V::to_f(V::from_f(x1 * V::to_f(s[i + half])));
+    dst[i] = V::from_f(a1 + b1);
+    dst[i + half] = V::from_f(a2 + b2);
+  }
+}
+
 }  // namespace cats

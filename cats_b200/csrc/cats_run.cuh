@@ -80,12 +80,18 @@ struct MegaPlan {
 // dense tensor-core path (cats_dense.cuh): 16-bit types, H a multiple of 128, I a multiple of 64
 struct DensePlan {
   bool ok = false;
-  int grid = 0, box_rows = 0, S1 = 0, S2 = 0, Sf = 0, wait_kc = 0, fused = 0;
-  size_t smem1 = 0, smem2 = 0, smemf = 0;
+  int grid = 0, box_rows = 0, Sf = 0, wait_kc = 0;   // Sf: ring stages
+  size_t smemf = 0;
 };
 cudaError_t inst_dense(const DensePlan& p, const void* x, const void* Wg, const void* Wu, const void* Wd,
                        WsPtrs ws, int B, int H, int I, int dtype, float thr, void* out, int out_mode,
                        void* resid, void* x_next, const void* norm_w, float eps, cudaStream_t st);
+
+constexpr int kDenseStackMaxLayers = 80;   // layers per launch of the dense stack kernel
+cudaError_t inst_dense_stack(const DensePlan& p, int L, const void* const* Wg, const void* const* Wu,
+                             const void* const* Wd, const float* thr, void* x_io, void* x_tmp,
+                             void* resid, WsPtrs ws, int B, int H, int I, int dtype, float eps,
+                             cudaStream_t st);
 
 // ---- launchers, one set per element type T (float, __half, __nv_bfloat16) -----------------------
 template <typename T>

@@ -100,7 +100,7 @@ class CatsDecoder:
         self.h = z(batch, self.H)                       # residual stream of the current token
         self.x = z(batch, self.H)                       # normalised input of the next block
         self.x2 = z(batch, self.H)
-        self.attn = z(batch, self.H)
+        self.q = z(batch, self.nh, self.hd)
         self.logits = z(batch, cfg.vocab_size)          # logits of the latest step (static buffer)
         self.ar = torch.arange(self.max_len, device=self.dev)
         self.out_tokens: List[torch.Tensor] = []
@@ -126,12 +126,17 @@ class CatsDecoder:
     def _attn_decode(self, l: int, x: torch.Tensor, bucket: int, cos, sin, mask) -> torch.Tensor:
         B, nh, nkv, hd = self.B, self.nh, self.nkv, self.hd
         qkv = F.linear(x, self.wqkv[l])
-        q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], -1)
-        q, k = q.view(B, nh, hd), k.view(B, nkv, hd)
-        q = q * cos + _rotate_half(q) * sin
-        k = k * cos + _rotate_half(k) * sin
-        self.kc[l].index_copy_(2, self.pos, k.unsqueeze(2))
-        self.vc[l].index_copy_(2, self.pos, v.reshape(B, nkv, 1, hd))
+        if self.dev.type == "cuda":
+            # RoPE + cache write in one launch (cats_rope_cache) instead of a dozen
+            q = self.q
+            ops.rope_cache(qkv, self.cos, self.sin, self.pos, q, self.kc[l], self.vc[l], nh, nkv)
+        else:
+            q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], -1)
+            q, k = q.view(B, nh, hd), k.view(B, nkv, hd)
+            q = q * cos + _rotate_half(q) * sin
+            k = k * cos + _rotate_half(k) * sin
+            self.kc[l].index_copy_(2, self.pos, k.unsqueeze(2))
+            self.vc[l].index_copy_(2, self.pos, v.reshape(B, nkv, 1, hd))
         o = F.scaled_dot_product_attention(q.unsqueeze(2), self.kc[l][:, :, :bucket],
                                            self.vc[l][:, :, :bucket], attn_mask=mask,
                                            enable_gqa=nh != nkv)

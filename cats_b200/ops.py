@@ -395,6 +395,30 @@ def tail(y: torch.Tensor, resid: torch.Tensor, x_next: Optional[torch.Tensor] = 
                                         _stream(dev)), "cats_tail")
 
 
+def rope_cache(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
+               q_out: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, n_heads: int,
+               n_kv_heads: int) -> None:
+    """RoPE of one new position's query / key heads and the KV-cache write (``cats_rope_cache``).
+    qkv (B, (nh + 2 nkv) hd); cos, sin (max_len, hd); pos: int64 CUDA tensor with one element;
+    q_out (B, nh, hd); kc, vc (B, nkv, max_len, hd)."""
+    _req(qkv, "qkv")
+    dev, dt = qkv.device, qkv.dtype
+    for t, name in ((cos, "cos"), (sin, "sin"), (q_out, "q_out"), (kc, "key cache"), (vc, "value cache")):
+        _req(t, name, dt, dev)
+    if pos.dtype != torch.int64 or pos.device != dev or pos.numel() != 1:
+        raise RuntimeError("cats_b200: pos must be a one-element int64 tensor on the same device")
+    B, nkv, max_len, hd = kc.shape
+    if tuple(vc.shape) != tuple(kc.shape) or nkv != n_kv_heads or qkv.numel() != B * (n_heads + 2 * nkv) * hd \
+            or q_out.numel() != B * n_heads * hd or tuple(cos.shape) != (max_len, hd) \
+            or tuple(sin.shape) != (max_len, hd):
+        raise RuntimeError("cats_b200: rope_cache shapes do not fit together")
+    with _on(dev):
+        _lib.check(_lib.lib().cats_rope_cache(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                              pos.data_ptr(), q_out.data_ptr(), kc.data_ptr(),
+                                              vc.data_ptr(), B, n_heads, nkv, hd, max_len,
+                                              dtype_code(dt), _stream(dev)), "cats_rope_cache")
+
+
 def transpose(src: torch.Tensor) -> torch.Tensor:
     """(R, C) -> new contiguous (C, R) through ``cats_transpose``."""
     _req(src, "matrix")

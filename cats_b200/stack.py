@@ -23,7 +23,7 @@ from .synth import Layer
 
 class CatsMLPStack:
     """``dense``: None = decided by ``ops.use_dense(batch, sparsity)``; True / False force the
-    dense tensor-core path (one cooperative launch per layer, replayed from a CUDA graph) or the
+    dense tensor-core path (``cats_mlp_stack_dense``: one cooperative launch for the stack) or the
     sparse kernels."""
 
     def __init__(self, layers: Sequence[Layer], batch: int = 1, eps: float = 1e-6,
@@ -64,7 +64,8 @@ class CatsMLPStack:
         self.graph = None
         if self.dense:
             self._wd = [l.wd_contiguous() for l in self.layers]
-            self.launches_per_step = self.L
+            self._wd_ptrs = arr(*[w.data_ptr() for w in self._wd])
+            self.launches_per_step = (self.L + 79) // 80     # one cooperative launch per 80 layers
 
     def _dense_layers(self) -> None:
         cur, nxt = self.x, self.x_tmp
@@ -96,9 +97,12 @@ class CatsMLPStack:
     def run_device(self) -> None:
         """All layers on the state already in ``self.x`` / ``self.resid`` (device resident)."""
         if self.dense:
-            if self.graph is None:
-                self.capture()
-            self.graph.replay()
+            with ops._on(self.device):
+                _lib.check(_lib.lib().cats_mlp_stack_dense(
+                    self.L, self._wg, self._wu, self._wd_ptrs, self._thr, self.x.data_ptr(),
+                    self.x_tmp.data_ptr(), self.resid.data_ptr(), self.ws.ptr, self.ws.nbytes,
+                    self.B, self.H, self.I, self.code, self.eps, ops._stream(self.device)),
+                    "cats_mlp_stack_dense")
             return
         with ops._on(self.device):
             _lib.check(_lib.lib().cats_mlp_stack(

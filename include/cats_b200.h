@@ -78,11 +78,10 @@ int cats_sm_count(void);
  * cats_read_counters); waits for other ranks get four times the limit.  "xchg": how the ranks'
  * partial sums are combined in cats_tp_mlp_stack (0 = chosen by the number of ranks, 1 = every
  * CTA adds all ranks' partial sums, 2 = every CTA adds its own slice and publishes the total;
- * all ranks must use the same value).  "dense_fused" (0/1, default 1): cats_mlp_dense as one
- * cooperative launch (0: a gate/up launch and a down launch).  The same values are read
+ * all ranks must use the same value).  The same values are read
  * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
  * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS, CATS_B200_WAIT_MS
- * CATS_B200_XCHG and CATS_B200_DENSE_FUSED.
+ * and CATS_B200_XCHG.
  * No reference counterpart (the reference has no device-side waits; its error path is exit(-1),
  * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:25-33, 2397-2400).
  */
@@ -191,6 +190,16 @@ int cats_mlp_dense(const void* x, const void* Wg, const void* Wu, const void* Wd
                    int out_mode, void* resid, void* x_next, const void* norm_weight, float eps,
                    void* stream);
 int cats_dense_supported(int B, int H, int I, int dtype);
+
+/*
+ * cats_mlp_stack on the dense tensor-core path: L layers (Wd[l] is [H, I]) chained through the
+ * fused residual + RMS-norm tail in one cooperative launch per 80 layers, the weight stream kept
+ * full across layers.  Arguments as for cats_mlp_stack; restrictions as for cats_mlp_dense.
+ * No reference counterpart as one call (see cats_mlp_stack).
+ */
+int cats_mlp_stack_dense(int L, const void* const* Wg, const void* const* Wu, const void* const* Wd,
+                         const float* thresholds, void* x_io, void* x_tmp, void* resid, void* ws,
+                         size_t ws_bytes, int B, int H, int I, int dtype, float eps, void* stream);
 
 /*
  * cats_mlp for callers that are not able to allocate device memory.
@@ -331,6 +340,21 @@ int cats_down_dense(const void* inter, const void* Wd, int B, int H, int I, int 
  */
 int cats_tail(const void* y, void* resid, void* x_next, const void* norm_weight, float eps, int B,
               int H, int dtype, void* stream);
+
+/*
+ * Decode-step glue of a decoder layer, between the fused QKV projection and attention: rotate-half
+ * rotary embedding of the query and key heads of one new position per sequence, and the write of
+ * the rotated keys and the values into a static KV cache at *position (device memory, so the call
+ * can sit in a CUDA graph whose position advances).  qkv [B, (n_heads + 2 n_kv_heads) head_dim]
+ * (q, k, v heads in that order); cos / sin tables [max_len, head_dim]; q_out [B, n_heads,
+ * head_dim]; caches [B, n_kv_heads, max_len, head_dim].  Rounds to the storage type after every
+ * operation, like the elementwise launches it replaces.  Not on the MLP path: it exists so that
+ * the decode loop around the MLP (cats_b200/decoder.py) is not dominated by small launches; the
+ * reference leaves this to HF's modelling code.
+ */
+int cats_rope_cache(const void* qkv, const void* cos_table, const void* sin_table,
+                    const long long* position, void* q_out, void* k_cache, void* v_cache, int B,
+                    int n_heads, int n_kv_heads, int head_dim, int max_len, int dtype, void* stream);
 
 /* Transpose a [rows, cols] matrix into [cols, rows] (packs Wd [H,I] into WdT [I,H]). */
 int cats_transpose(const void* src, void* dst, int rows, int cols, int dtype, void* stream);

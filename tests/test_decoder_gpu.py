@@ -102,3 +102,33 @@ def test_hf_generate_runs_the_cuda_path_through_the_swapped_modules(cuda_device)
     assert calls["n"] >= 5                                   # every decode step after the prefill
     la, lb = torch.stack(outs[0].logits), torch.stack(outs[2].logits)
     assert O.rel_l2(to_np(lb[:2]), to_np(la[:2])) <= 3e-2   # first steps: same token history
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv", [(8, 8), (8, 2)])
+def test_rope_and_cache_write_equal_the_elementwise_launches(dt, nh, nkv, cuda_device):
+    from cats_b200 import ops
+    from cats_b200.decoder import _rotate_half
+
+    B, hd, max_len = 3, 128, 64
+    dev = cuda_device
+    torch.manual_seed(1)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev).to(dt)
+    ang = torch.outer(torch.arange(max_len, device=dev).float(), torch.rand(hd // 2, device=dev))
+    emb = torch.cat((ang, ang), -1)
+    cos, sin = emb.cos().to(dt), emb.sin().to(dt)
+    for p in (0, 17, max_len - 1):
+        pos = torch.tensor([p], device=dev)
+        kc = torch.zeros(B, nkv, max_len, hd, device=dev, dtype=dt)
+        vc = torch.zeros_like(kc)
+        q_out = torch.empty(B, nh, hd, device=dev, dtype=dt)
+        ops.rope_cache(qkv, cos, sin, pos, q_out, kc, vc, nh, nkv)
+        q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], -1)
+        q, k = q.view(B, nh, hd), k.view(B, nkv, hd)
+        c, s = cos[p:p + 1], sin[p:p + 1]
+        assert torch.equal(q_out, q * c + _rotate_half(q) * s)
+        assert torch.equal(kc[:, :, p], k * c + _rotate_half(k) * s)
+        assert torch.equal(vc[:, :, p], v.reshape(B, nkv, hd))
+        kc[:, :, p] = 0
+        vc[:, :, p] = 0
+        assert float(kc.abs().max()) == 0 and float(vc.abs().max()) == 0     # nothing else written

@@ -185,7 +185,7 @@ def test_lists_left_by_an_earlier_call_are_never_read(cuda_device):
         o_flat = up(o_gate + 4 * I * 16)
         o_h = up(o_flat + 4 * I)
         o_end = up(o_h + 4 * I * 16)
-        assert o_end == ws.nbytes
+        assert o_end + 48 * 1024 == ws.nbytes          # + the dense stack kernel's table
         for B in (1, 2, 1, 4):
             x, layer = synth_case(H, I, B, dt, 0.5, 11 + B, dev)
             ref = O.dense_masked_mlp(to_np(x).reshape(B, H), to_np(layer.wg), to_np(layer.wu),
