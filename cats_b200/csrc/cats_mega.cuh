@@ -88,6 +88,8 @@ struct MegaArgs {
   // p's exchange buffer as mapped into this process; xchg[rank] is local).  nranks == 0: none.
   int nranks, rank;
   int xchg_all;  // 1: every CTA adds all ranks' slots itself; 0: per-slice totals (see the lister)
+  int local;     // 1: every CTA works on its own segment's active neurons (no list barrier); needs
+                 //    nranks >= 1 and one part per layer
   unsigned char* xchg[kMaxRanks];
 };
 
@@ -321,7 +323,50 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         // this CTA's gate values of part h are in: ballot / popc compaction, publish, arrive
         if (ok) ok = mbar_wait(gdone_u + 8u * h, l & 1, &s_abort);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        if (ok && A.local) {
+          // Local lists (tensor-parallel ranks with a few rows per CTA): this CTA's own active
+          // neurons ARE its work list - straight into shared memory, no publication, no grid
+          // barrier, no scan.  The up / down rows are then not balanced over the CTAs, which
+          // costs less than the barrier chain it replaces when a CTA has a dozen rows.
+          if (l >= 1) ok = mbar_wait(lfree_u + 8u * h, (l - 1) & 1, &s_abort);  // list h is free
+          ok = __all_sync(0xffffffffu, ok);
+          const int r0 = seg_lo(h), R = seg_hi(h) - r0;
+          const float* sv = s_val + (size_t)h * A.rmax * BT;
+          int base = 0;
+          for (int g0 = 0; g0 < R && ok; g0 += 32) {
+            const int lr = g0 + lane;
+            float v[BT];
+            bool any = false;
+#pragma unroll
+            for (int t = 0; t < BT; ++t) {
+              v[t] = 0.f;
+              if (lr < R && t < B) {
+                const float sval = sv[lr * BT + t];
+                const bool a = is_active(sval, thr);
+                v[t] = a ? sval : 0.f;
+                any |= a;
+              }
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, any);
+            if (any) {
+              const int pos = base + __popc(m & ((1u << lane) - 1u));
+              s_idx[h * A.cap + pos] = r0 + lr;
+#pragma unroll
+              for (int t = 0; t < BT; ++t) s_hg[(h * A.cap + pos) * BT + t] = v[t];
+            }
+            base += __popc(m);
+          }
+          if (lane == 0) {
+            s_cnt[h] = ok ? base : 0;
+            ws.seg_count[h * kSegHalfStride + c] = base;
+          }
+          // the lister's clearing of this CTA's accumulator slice (layer l-1's exchange) is
+          // ordered ahead of everything this CTA publishes for layer l
+          if (ok && l >= 1) ok = mbar_wait(zdone_u, (l - 1) & 1, &s_abort);
+          ok = __all_sync(0xffffffffu, ok);
+          __syncwarp();
+          if (lane == 0 && ok) mbar_arrive(lready_u + 8u * h);
+        } else if (ok) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
           const float* sv = s_val + (size_t)h * A.rmax * BT;
           int base = 0;
@@ -363,7 +408,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     // =========================================================================== lister
     bool ok = true;
     for (int l = 0; l < L; ++l) {
-      for (int h = 0; h < NP; ++h) {
+      for (int h = 0; h < (A.local ? 0 : NP); ++h) {
         // all CTAs have published part h: scan the counts, take this CTA's balanced share
         if (ok) ok = grid_wait(gbar + h, gtarget(l), &s_abort);
         ok = __all_sync(0xffffffffu, ok);
@@ -481,6 +526,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           ok = __all_sync(0xffffffffu, good);
           __threadfence();  // the cleared slice, ahead of this warp's next barrier hand-offs
         }
+        __syncwarp();
+        if (A.local && lane == 0 && ok) mbar_arrive(zdone_u);   // (the publisher waits for it)
       } else if (l >= 1) {
         // Every CTA has read layer l-1's accumulators (it needed x_l for gate rows that are
         // published by now): clear this CTA's slice so that layer l+1 can add into them.
@@ -898,7 +945,9 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         if (K) xflag[XCH_LAYERS] = xl0 + (unsigned)L;
         ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)L * (unsigned)G);
         ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
-        ws.hdr[HDR_NSEG] = -1;  // this kernel's segment lists are per half: not resumable
+        // segment counts are per part (not a flat list); with local lists they are this layer's
+        // per-CTA counts and add up to the number of active neurons
+        ws.hdr[HDR_NSEG] = A.local ? G : -1;
       }
     }
   }

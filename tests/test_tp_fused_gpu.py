@@ -23,7 +23,11 @@ def to_np(t):
 
 @pytest.mark.parametrize("H,I,L,B,dt", [(1024, 2752, 5, 1, torch.float16),
                                         (4096, 14336, 3, 2, torch.bfloat16),
-                                        (2048, 4096, 4, 4, torch.float32)])
+                                        (2048, 4096, 4, 4, torch.float32),
+                                        # a rank's slice of an 8-way split: 12 rows per CTA, one
+                                        # part per layer, every CTA on its own rows' list
+                                        (4096, 1792, 6, 1, torch.float16),
+                                        (1024, 1792, 4, 2, torch.float32)])
 def test_single_rank_exchange_matches_the_plain_stack_and_the_oracle(H, I, L, B, dt, cuda_device):
     from cats_b200 import synth, tp
     from cats_b200.stack import CatsMLPStack
