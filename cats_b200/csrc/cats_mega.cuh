@@ -102,7 +102,14 @@ struct MegaArgs {
 // two pairs per instruction, each element single-copy atomic in the PTX memory model), so a
 // reader that finds the tag it expects has the value that belongs to it: no fence and no flag
 // orders data against anything, on either side; a pair that has not arrived is read again.
-enum { XCH_LAYERS = 0, XCH_HDR_BYTES = 256 };
+// Besides the tags there are arrival counters - HINTS that spare the readers from polling the
+// data itself: one per source rank (a source's CTAs bump it over NVLink after their stores into
+// this buffer) and one for the totals (bumped by this GPU's own CTAs); XCH_BASE is their common
+// value at the start of the launch.  The bumps are relaxed and not ordered against the data:
+// a reader that saw the counter still checks every tag, and a reader whose counter wait runs
+// out falls back to polling the tags.
+enum { XCH_LAYERS = 0, XCH_BASE = 1, XCH_ARRIVED = 8 /* [kMaxRanks] */, XCH_SUMS = 16,
+       XCH_HDR_BYTES = 256 };
 constexpr int kMegaMaxB = 4;
 __host__ __device__ inline size_t xchg_bytes(int H) {
   return XCH_HDR_BYTES + sizeof(uint2) * 2 * (size_t)(kMaxRanks + 1) * kMegaMaxB * H;
@@ -139,6 +146,27 @@ __device__ __forceinline__ bool pair_has(unsigned long long a, unsigned tag) {
 }
 __device__ __forceinline__ float pair_val(unsigned long long a) {
   return __uint_as_float((unsigned)a);
+}
+__device__ __forceinline__ void bump_relaxed_sys(unsigned* ctr) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+}
+__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Wait (bounded, never aborting: it is only a hint) until the counter has reached `target`.
+__device__ __forceinline__ void hint_wait(const unsigned* ctr, unsigned target, volatile int* abort) {
+  if ((int)(ld_relaxed_sys(ctr) - target) >= 0) return;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if ((int)(ld_relaxed_sys(ctr) - target) >= 0) return;
+      __nanosleep(40);
+    }
+    if (*abort || clock64() - t0 > wait_limit(abort)) return;
+  }
 }
 // Four consecutive pairs (one group of four columns) with the tag `tag`, re-read until every one
 // of them has arrived; bounded like every wait.  False when the limit ran out.
@@ -232,6 +260,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   const int K = A.nranks;
   unsigned* xflag = K ? reinterpret_cast<unsigned*>(A.xchg[A.rank]) : nullptr;
   const unsigned xl0 = K ? __ldcg(xflag + XCH_LAYERS) : 0u;
+  const unsigned xbase = K ? __ldcg(xflag + XCH_BASE) : 0u;
   // this CTA's slice (groups of 4 columns) of a [B, H] vector
   const int ngrp_all = H >> 2;
   const int own_lo = (int)(((long long)ngrp_all * c) / G),
@@ -493,6 +522,8 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
               st_pairs(dst + 2, q2, q3);
             }
           }
+          __syncwarp();
+          if (lane < K) bump_relaxed_sys(reinterpret_cast<unsigned*>(A.xchg[lane]) + XCH_ARRIVED + A.rank);
           bool good = true;
           for (int e = lane; e < B * own_n && !A.xchg_all; e += 32) {
             const int b = e / own_n, g = own_lo + (e - b * own_n);
@@ -524,6 +555,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
             }
           }
           ok = __all_sync(0xffffffffu, good);
+          if (lane == 0 && ok) bump_relaxed_sys(xflag + XCH_SUMS);   // (in both modes: one base)
           __threadfence();  // the cleared slice, ahead of this warp's next barrier hand-offs
         }
         __syncwarp();
@@ -557,6 +589,15 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       // tensor parallel: the ranks' totals arrive slice by slice as tagged pairs (see the lister)
       if (!K) {
         if (tid == 0 && ok) grid_wait(obar, otarget(l), &s_abort);
+      } else if (ok) {
+        // hints: every source rank's CTAs (or this GPU's own, for the totals) have bumped their
+        // counter - the data is most probably there, the tags below decide
+        const unsigned target = xbase + (unsigned)(l + 1) * (unsigned)G;
+        if (A.xchg_all) {
+          if (tid < K) hint_wait(xflag + XCH_ARRIVED + tid, target, &s_abort);
+        } else if (tid == 0) {
+          hint_wait(xflag + XCH_SUMS, target, &s_abort);
+        }
       }
       consumer_bar_sync();
       ok = !s_abort;
@@ -942,8 +983,12 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         for (int e = lo + tid; e < hi; e += kConsumerThreads) accp[e] = 0.f;
       }
       if (c == 0 && tid == 0) {
-        if (K) xflag[XCH_LAYERS] = xl0 + (unsigned)L;
-        ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (unsigned)L * (unsigned)G);
+        if (K) {
+          xflag[XCH_LAYERS] = xl0 + (unsigned)L;
+          xflag[XCH_BASE] = xbase + (unsigned)L * (unsigned)G;
+        }
+        // (with local lists nobody arrived at the list barriers: their counters did not move)
+        ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (A.local ? 0u : (unsigned)L * (unsigned)G));
         ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
         // segment counts are per part (not a flat list); with local lists they are this layer's
         // per-CTA counts and add up to the number of active neurons

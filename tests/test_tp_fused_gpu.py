@@ -89,6 +89,14 @@ def test_bad_rank_arguments_are_refused_on_the_host(cuda_device):
     assert call(1, 0, [xb.data_ptr()]) == _lib.OK
     torch.cuda.synchronize()
     assert ws.counters()[1] == 0
+    # the same workspace serves the other entry points afterwards (its barrier counters and
+    # accumulators are left consistent whichever schedule the tensor-parallel launch took)
+    from oracle import cats_oracle as O2
+    out = ops.mlp(x.reshape(B, 1, H), layers[0].wg, layers[0].wu, layers[0].wdt, layers[0].threshold, ws=ws)
+    ref = O2.dense_masked_mlp(to_np(x), to_np(layers[0].wg), to_np(layers[0].wu), to_np(layers[0].wdt).T,
+                              layers[0].threshold)
+    assert O2.rel_l2(to_np(out).reshape(B, H), ref["out"]) <= 1e-2
+    assert ws.counters()[1] == 0
 
 
 def test_a_wait_that_runs_out_ends_the_kernel_with_a_status_and_recovery_works(cuda_device):
