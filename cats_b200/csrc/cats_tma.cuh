@@ -553,37 +553,56 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
     }
     consumer_bar_sync();  // every h_j of this CTA is final
     ok = ok && !s_abort;
-    // down rows
-    float acc[NVT][N][BT];
+    // Down rows in groups of kDG: lane q waits for the q-th row of the group (one round trip to
+    // the barrier unit per group instead of one per row), every thread loads the group's vectors
+    // of its columns before the first FMA, then lane q releases the q-th stage.  16-bit weights
+    // go through the mixed-precision FMAs (no conversion instructions), as in the persistent
+    // kernel.
+    float acc[NVT][BT][N];
 #pragma unroll
     for (int g = 0; g < NVT; ++g)
 #pragma unroll
-      for (int i = 0; i < N; ++i)
+      for (int t = 0; t < BT; ++t)
 #pragma unroll
-        for (int t = 0; t < BT; ++t) acc[g][i][t] = 0.f;
-    for (int k = cnt; k < nitems && ok; ++k) {
-      const int s = k % S;
-      ok = mbar_wait_warp(full_u + 8u * s, (k / S) & 1, &s_abort);
-      if (ok) {
-        const uint4* row = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
-        float hb[BT];
+        for (int i = 0; i < N; ++i) acc[g][t][i] = 0.f;
+    constexpr int kDG = (NVT * BT * N > 64) ? 4 : 8;   // fewer rows in flight where the accumulators fill the registers
+    const int dg = S < kDG ? S : kDG;                   // a group must fit in the ring
+    for (int j0 = 0; j0 < cnt && ok; j0 += dg) {
+      const int nb = (cnt - j0) < dg ? (cnt - j0) : dg;
+      bool mine = true;
+      int my_slot = 0;
+      if (lane < nb) {
+        const int kk = cnt + j0 + lane;
+        my_slot = kk % S;
+        mine = mbar_wait(full_u + 8u * my_slot, (kk / S) & 1, &s_abort);
+      }
+      ok = __all_sync(0xffffffffu, mine);
+      if (!ok) break;
+      typename V::Scalar hb[kDG][BT];
+      const uint4* rowp[kDG];
 #pragma unroll
-        for (int t = 0; t < BT; ++t) hb[t] = s_h[(k - cnt) * BT + t];
+      for (int q = 0; q < kDG; ++q) {
+        const int qq = q < nb ? q : 0;
+        const int slot = __shfl_sync(0xffffffffu, my_slot, qq);
+        rowp[q] = reinterpret_cast<const uint4*>(ring + (size_t)slot * row_bytes);
 #pragma unroll
-        for (int g = 0; g < NVT; ++g) {
-          const int v = g * kConsumerThreads + tid;
-          if (v < nvec) {
-            float wf[N];
-            V::unpack(row[v], wf);
+        for (int t = 0; t < BT; ++t) hb[q][t] = V::prep(q < nb ? s_h[(j0 + q) * BT + t] : 0.f);
+      }
 #pragma unroll
-            for (int i = 0; i < N; ++i)
+      for (int g = 0; g < NVT; ++g) {
+        const int v = g * kConsumerThreads + tid;
+        if (v < nvec) {
+          uint4 wq[kDG];
 #pragma unroll
-              for (int t = 0; t < BT; ++t) acc[g][i][t] = fmaf(hb[t], wf[i], acc[g][i][t]);
-          }
+          for (int q = 0; q < kDG; ++q) wq[q] = rowp[q][v];
+#pragma unroll
+          for (int q = 0; q < kDG; ++q)
+#pragma unroll
+            for (int t = 0; t < BT; ++t) V::axpy(hb[q][t], wq[q], acc[g][t]);
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_u + 8u * s);
+      if (lane < nb) mbar_arrive(empty_u + 8u * my_slot);
     }
     if (cnt > 0) {
 #pragma unroll
@@ -596,8 +615,8 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
               float* dst = ws.acc32 + (size_t)t * H + (size_t)v * N;
 #pragma unroll
               for (int i = 0; i < N; i += 4)
-                red_add_v4(dst + i, acc[g][i][t], acc[g][i + 1][t], acc[g][i + 2][t],
-                           acc[g][i + 3][t]);
+                red_add_v4(dst + i, acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2],
+                           acc[g][t][i + 3]);
             }
           }
         }
