@@ -285,6 +285,31 @@ def per_launch_us(launch_one, n_items, repeats, stream, before=None):
             math.exp(statistics.mean(math.log(max(t, 1e-3)) for t in ts)))
 
 
+def graph_launch_us(launch_one, n_items, repeats, stream):
+    """Mean duration of one launch when ``n_items`` launches (one per layer, so every launch reads
+    weights that are not in L2) replay back to back from a CUDA graph: what the kernel takes when
+    the host is not the limit (a Python call per launch costs as much as these kernels run).
+    Returns a 1-tuple to read like per_launch_us()[0]."""
+    launch_one(0)
+    stream.synchronize()
+    side = torch.cuda.Stream()             # capture needs a stream other than the default one
+    side.wait_stream(stream)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i in range(n_items):
+            launch_one(i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(side):
+        g.replay()
+        side.synchronize()
+        e0.record(side)
+        for _ in range(repeats):
+            g.replay()
+        e1.record(side)
+    side.synchronize()
+    return (e0.elapsed_time(e1) * 1e3 / (repeats * n_items),)
+
+
 class Dist:
     """The process group of this run (or none), with the two operations the bench needs."""
 
@@ -805,11 +830,11 @@ def run_gpu_arm(args):
     staged = None
     if B <= 4 and not dense_path:
         reps = max(1, min(10, 320 // L))
-        gate_us = per_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
-                                L, reps, stream)
-        ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
-        updown_us = per_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
+        gate_us = graph_launch_us(lambda i: ops.gate(xin, layers[i].wg, layers[i].threshold, ws=ws),
                                   L, reps, stream)
+        ops.gate(xin, layers[0].wg, layers[0].threshold, ws=ws)
+        updown_us = graph_launch_us(lambda i: ops.updown(xin, layers[i].wu, layers[i].wdt, ws, out=out),
+                                    L, reps, stream)
         staged = {
             "k_gate_tma": {"us": gate_us[0], "bytes": bytes_gate, "GBps": bytes_gate / gate_us[0] / 1e3},
             "k_updown_tma": {"us": updown_us[0], "bytes": bytes_updown,

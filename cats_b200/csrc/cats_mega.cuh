@@ -759,7 +759,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
 
     for (int l = 0; l < L; ++l) {
       if (l > 0) next_x(l - 1, false);
-      const float thr = P.thr[l];
 #pragma unroll
       for (int g = 0; g < NVT; ++g)
 #pragma unroll
