@@ -104,6 +104,7 @@ struct Options {
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
   int wait_ms = 1000;  // limit of every device-side wait (mbarrier, grid barrier, peer data)
+  int l2_ahead_kb = 128;  // gate rows a stalled producer of the persistent kernel asks into L2, KB per CTA (0: off)
   int local_lists = 1; // tensor-parallel ranks with one part per layer: per-CTA lists, no list barrier
   int xchg = 0;        // tensor-parallel exchange: 0 = by the number of ranks, 1 = every CTA adds
                        // all ranks' partial sums, 2 = per-slice totals published by each CTA
@@ -121,6 +122,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_WAIT_MS")) v.wait_ms = atoi(e);
     if (const char* e = getenv("CATS_B200_XCHG")) v.xchg = atoi(e);
     if (const char* e = getenv("CATS_B200_LOCAL_LISTS")) v.local_lists = atoi(e);
+    if (const char* e = getenv("CATS_B200_L2_AHEAD_KB")) v.l2_ahead_kb = atoi(e);
     return v;
   }();
   return o;
@@ -314,6 +316,7 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   A.parts = p.parts;
   A.wait_kc = wait_kcycles();
   A.s_magic = (unsigned)(0x100000000ull / (unsigned)p.S) + 1u;
+  A.pf_rows = options().l2_ahead_kb > 0 ? (int)((size_t)options().l2_ahead_kb * 1024 / ((size_t)A.H * esize(dtype))) : 0;
   A.cap = p.cap;
   A.rmax = p.rmax;
   CATS_DISPATCH(dtype, inst_mega, p, P, A, ws, st);
@@ -413,6 +416,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "wait_ms")) options().wait_ms = value;
   else if (!strcmp(name, "xchg")) options().xchg = value;
   else if (!strcmp(name, "local_lists")) options().local_lists = value;
+  else if (!strcmp(name, "l2_ahead_kb")) options().l2_ahead_kb = value;
   else return CATS_ERR_MODE;
   return CATS_OK;
 }

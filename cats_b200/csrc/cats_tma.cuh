@@ -85,6 +85,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// The same wait, with a call of `on_stall()` once the wait has lasted `stall_cycles`: a producer
+// that stands that long is not held up by the ring's ordinary back-pressure but by consumers at a
+// grid barrier, and can use the time.
+template <typename F>
+__device__ __forceinline__ bool mbar_wait_or(uint32_t bar, uint32_t parity, volatile int* abort,
+                                             long long stall_cycles, F&& on_stall) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  bool told = false;
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+    const long long dt = clock64() - t0;
+    if (!told && dt > stall_cycles) {
+      told = true;
+      on_stall();
+    }
+    if (dt > 20000) __nanosleep(100);
+    if (dt > wait_limit(abort)) {
+      *abort = 1;
+      return false;
+    }
+  }
+}
+// Ask for `bytes` (a multiple of 16, 16-byte aligned) of global memory to be brought into L2.
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // Whole-warp wait: lane 0 polls, the result is broadcast.  One polling lane per warp instead of
 // 32 keeps the shared-memory pipe free for the warps that are working (32 lanes polling one
 // barrier word serialise into 32 accesses per poll).  Must be called by a converged warp.

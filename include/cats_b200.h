@@ -80,11 +80,13 @@ int cats_sm_count(void);
  * CTA adds all ranks' partial sums, 2 = every CTA adds its own slice and publishes the total;
  * all ranks must use the same value).  "local_lists" (0/1, default 1): in cats_tp_mlp_stack, when
  * a rank's slice leaves a CTA too few rows to split a layer into parts, every CTA works on the
- * active neurons of its own rows (no list barrier) instead of a balanced share.  The same values
- * are read
+ * active neurons of its own rows (no list barrier) instead of a balanced share.  "l2_ahead_kb"
+ * (default 128, 0 = off): how many KiB of its coming gate rows a CTA of the persistent kernel asks
+ * into L2 when its copy ring has stood still for about two microseconds (the consumers are at a
+ * grid barrier then and HBM would idle).  The same values are read
  * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
  * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS, CATS_B200_WAIT_MS
- * CATS_B200_XCHG and CATS_B200_LOCAL_LISTS.
+ * CATS_B200_XCHG, CATS_B200_LOCAL_LISTS and CATS_B200_L2_AHEAD_KB.
  * No reference counterpart (the reference has no device-side waits; its error path is exit(-1),
  * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:25-33, 2397-2400).
  */
