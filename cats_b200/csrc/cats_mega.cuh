@@ -282,10 +282,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     s_ctl[1] = A.wait_kc;
     mbar_fence_init();
   }
-  for (int b = 0; b < B; ++b)
-    stage_x<T>(reinterpret_cast<const T*>(A.x_in) + (size_t)b * H, xs + (size_t)b * xs_ld, 1, H);
-  if (has_resid) stage_x<T>(reinterpret_cast<const T*>(A.resid), rs, B, H);
-  __syncthreads();
+  __syncthreads();  // the barriers exist; the producers go straight to their copies
 
   // this CTA's gate segment of half h
   auto seg_lo = [&](int h) {
@@ -623,6 +620,23 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
     bool ok = true;
     int k = 0;
     float acc[NVT][BT][N];
+
+    // Only the consumers read x and the residual: they stage them while the first gate rows are
+    // already on their way.
+    {
+      const int nv = H / N;
+      for (int b = 0; b < B; ++b) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(A.x_in) + (size_t)b * H);
+        uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)b * xs_ld);
+        for (int i = tid; i < nv; i += kConsumerThreads) dst[i] = __ldcg(src + i);
+      }
+      if (has_resid) {
+        const uint4* src = reinterpret_cast<const uint4*>(A.resid);
+        uint4* dst = reinterpret_cast<uint4*>(rs);
+        for (int i = tid; i < B * nv; i += kConsumerThreads) dst[i] = __ldcg(src + i);
+      }
+      consumer_bar_sync();
+    }
 
     // x_{l+1} (and, after the last layer, the outputs) from layer l's accumulators.  Every CTA
     // computes the whole vector for itself; global outputs are written in disjoint slices.
