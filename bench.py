@@ -590,18 +590,36 @@ def single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act, esize, pea
 
     from cats_b200 import ops
 
+    from cats_b200 import _lib
+
     L = len(layers)
     xin = x0.reshape(B, 1, H).contiguous()
     out = torch.empty_like(xin)
     call = lambda i: ops.mlp(xin, layers[i].wg, layers[i].wu, layers[i].wdt, layers[i].threshold,
                              out=out, ws=ws)
-    for i in range(min(L, 4)):
-        call(i)
-    reps = max(1, 128 // L)
-    b2b = per_launch_us(call, L, reps, stream)
     by = esize * I * H + 2 * esize * n_act * H + 4 * esize * B * H
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=xin.device)
-    fl = per_launch_us(call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
+    row = lambda t: {"mean_us": t[0], "median_us": t[1], "min_us": t[2], "geomean_us": t[3]}
+    dcode = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+    routes = {}
+    # the two routes cats_mlp has for one token: the stage-1 / stage-2+3 kernel pair with
+    # programmatic dependent launch (default) and a single-layer launch of the persistent kernel
+    for name, pair in (("kernel_pair", 1), ("persistent_kernel", 0)):
+        _lib.check(_lib.lib().cats_set_option(b"single_pair", pair))
+        if name == "kernel_pair" and _lib.lib().cats_uses_persistent_kernel(1, B, H, I, dcode):
+            continue                                   # this shape or batch has no pair route
+        for i in range(min(L, 4)):
+            call(i)
+        b2b = per_launch_us(call, L, max(1, 128 // L), stream)
+        gr = graph_launch_us(call, L, max(1, 128 // L), stream)
+        fl = per_launch_us(call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
+        routes[name] = {
+            "back_to_back": dict(row(b2b), GBps=by / b2b[1] / 1e3, frac_of_peak=by / b2b[1] / 1e3 / peak),
+            "graph_replay_us": gr[0], "graph_replay_frac_of_peak": by / gr[0] / 1e3 / peak,
+            "reference_protocol": row(fl)}
+    _lib.check(_lib.lib().cats_set_option(b"single_pair", 1))
+    default = "kernel_pair" if "kernel_pair" in routes else "persistent_kernel"
+    fl = tuple(routes[default]["reference_protocol"][k] for k in ("mean_us", "median_us", "min_us", "geomean_us"))
     k = (int(round(n_act)) + 7) // 8 * 8      # whole 16-byte vectors of fp16, as cuBLAS likes them
     dense_call = lambda i: F.linear(F.silu(F.linear(xin, layers[i].wg)) * F.linear(xin, layers[i].wu),
                                     layers[i].wdt.t())
@@ -612,10 +630,13 @@ def single_layer_block(layers, x0, B, H, I, dtype, ws, stream, n_act, esize, pea
     dn = per_launch_us(dense_call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
     op = per_launch_us(opt_call, L, max(1, 100 // L + 1), stream, before=flush.zero_)
     del flush
-    row = lambda t: {"mean_us": t[0], "median_us": t[1], "min_us": t[2], "geomean_us": t[3]}
     return {
-        "what": "one cats_mlp call per layer (single-layer launch of the persistent kernel)",
-        "back_to_back": dict(row(b2b), GBps=by / b2b[1] / 1e3, frac_of_peak=by / b2b[1] / 1e3 / peak),
+        "what": "one cats_mlp call per layer, both routes: back to back with an event pair per call, "
+                "replayed from a CUDA graph of all layers (how a decoder runs it), and under the "
+                "reference's micro-benchmark protocol",
+        "default_route": default,
+        "routes": routes,
+        "back_to_back": routes[default]["back_to_back"],
         "reference_protocol": {
             "protocol": "L2 flush (512 MB zero_) before every call, per-call CUDA events, geometric "
                         "mean (flash_gemv/bench/utils.py:12-58)",

@@ -100,6 +100,7 @@ struct Options {
   int use_tma = 1;     // TMA-fed kernels where the shape allows (else the direct-load kernels)
   int ring_kb = 200;   // shared-memory ring per TMA kernel
   int use_mega = 1;    // persistent cooperative kernel for cats_mlp / cats_mlp_stack
+  int single_pair = 1; // cats_mlp with one token: the stage-1 / stage-2+3 kernel pair instead
   int bulk_flush = 1;  // persistent kernel: flush accumulators with TMA bulk reduces
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
   int parts = 0;       // persistent kernel: parts per layer (0 = choose by the rows per CTA)
@@ -116,6 +117,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_RING_KB")) v.ring_kb = atoi(e);
     if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
     if (const char* e = getenv("CATS_B200_MEGA")) v.use_mega = atoi(e);
+    if (const char* e = getenv("CATS_B200_SINGLE_PAIR")) v.single_pair = atoi(e);
     if (const char* e = getenv("CATS_B200_BULK_FLUSH")) v.bulk_flush = atoi(e);
     if (const char* e = getenv("CATS_B200_MMA_DOT")) v.mma_dot = atoi(e);
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
@@ -322,6 +324,18 @@ cudaError_t do_mega(const MegaPlan& p, const MegaParams& P, MegaArgs A, WsPtrs w
   CATS_DISPATCH(dtype, inst_mega, p, P, A, ws, st);
 }
 
+// One layer, one token: which kernels cats_mlp launches.  The persistent kernel is a cooperative
+// launch: it cannot overlap its start with the end of the kernel before it, and inside a decoder
+// (attention kernels before and after every MLP) that costs more than its better streaming
+// gains on a single layer.  The stage-1 / stage-2+3 pair is launched with programmatic dependent
+// launch and runs a decoder's token 5-6 % faster (measured, Llama-2-7B and Mistral-7B shapes), so
+// it is the default there; timed alone with an event pair per call the persistent kernel is
+// 2-3 % ahead.  Stacks of layers (cats_mlp_stack) always take the persistent kernel.
+bool single_layer_pair(int B, int H, int I, int dtype) {
+  if (B != 1 || !options().single_pair || !options().use_tma) return false;
+  return plan_gate_tma(B, H, I, dtype).ok && plan_updown_tma(B, H, I, dtype).ok;
+}
+
 // Dense tensor-core path: one row tile of at most 128 neurons per CTA and pass (two passes at the
 // 70B shape), rings as deep as shared memory allows.
 DensePlan plan_dense(int B, int H, int I, int dtype) {
@@ -410,6 +424,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "ring_kb")) options().ring_kb = value;
   else if (!strcmp(name, "pdl")) g_use_pdl = value;
   else if (!strcmp(name, "mega")) options().use_mega = value;
+  else if (!strcmp(name, "single_pair")) options().single_pair = value;
   else if (!strcmp(name, "bulk_flush")) options().bulk_flush = value;
   else if (!strcmp(name, "mma_dot")) options().mma_dot = value;
   else if (!strcmp(name, "parts")) options().parts = value;
@@ -518,7 +533,7 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
   WsPtrs p;
   if ((s = check_ws(ws, ws_bytes, H, I, &p))) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (out_mode == CATS_OUT_STORE) {
+  if (out_mode == CATS_OUT_STORE && !single_layer_pair(B, H, I, dtype)) {
     const MegaPlan mp = plan_mega(1, B, H, I, dtype, resid != nullptr);
     if (mp.ok) {
       MegaParams P;
@@ -719,6 +734,7 @@ int cats_tp_mlp_stack(int L, const void* const* Wg, const void* const* Wu, const
 
 int cats_uses_persistent_kernel(int L, int B, int H, int I, int dtype) {
   if (check_common(B, H, I, dtype)) return 0;
+  if (L == 1 && single_layer_pair(B, H, I, dtype)) return 0;
   return plan_mega(L, B, H, I, dtype, true).ok ? 1 : 0;
 }
 

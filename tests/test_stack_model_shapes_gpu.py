@@ -46,13 +46,19 @@ def chain_tol(dt, L):
 
 
 def chain_of_single_launches(layers, x0, B, H, eps=1e-6):
-    from cats_b200 import ops
+    """The persistent kernel, one layer per launch (for one token cats_mlp would otherwise take the
+    stage-1 / stage-2+3 kernel pair, whose sums run in another order)."""
+    from cats_b200 import _lib, ops
 
     x, r = x0.clone(), x0.clone()
     nxt = torch.empty_like(x)
-    for l in layers:
-        ops.mlp(x.reshape(B, 1, H), l.wg, l.wu, l.wdt, l.threshold, resid=r, x_next=nxt, eps=eps)
-        x, nxt = nxt, x
+    assert _lib.lib().cats_set_option(b"single_pair", 0) == 0
+    try:
+        for l in layers:
+            ops.mlp(x.reshape(B, 1, H), l.wg, l.wu, l.wdt, l.threshold, resid=r, x_next=nxt, eps=eps)
+            x, nxt = nxt, x
+    finally:
+        assert _lib.lib().cats_set_option(b"single_pair", 1) == 0
     return x, r
 
 
@@ -89,6 +95,44 @@ def test_stack_at_model_shape_twice_on_one_workspace(H, I, L, B, dt, sparsity, c
         xe, re_, _ = O.mlp_stack(to_np(x0), np_layers, thr, round_to=ROUND[dt])
         assert O.rel_l2(to_np(stack.resid), re_) <= ORACLE_TOL[dt], (seed, "resid")
         assert O.rel_l2(to_np(stack.x), xe) <= ORACLE_TOL[dt], (seed, "x")
+
+
+@pytest.mark.parametrize("pair", [1, 0])
+@pytest.mark.parametrize("H,I,dt", [
+    (4096, 14336, torch.float16), (4096, 14336, torch.bfloat16), (4096, 11008, torch.float32),
+    (8192, 28672, torch.bfloat16),
+])
+def test_both_single_layer_routes_at_model_shape(H, I, dt, pair, cuda_device):
+    """cats_mlp for one token: the kernel pair with programmatic dependent launch (the default) and
+    the persistent kernel (option single_pair = 0), each with the fused residual + RMS-norm tail,
+    against the oracle; twice on one workspace."""
+    from cats_b200 import _lib, ops, synth
+    from test_parity_gpu import run_and_check
+
+    L = _lib.lib()
+    dcode = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dt]
+    assert L.cats_set_option(b"single_pair", pair) == 0
+    try:
+        assert L.cats_uses_persistent_kernel(1, 1, H, I, dcode) == (0 if pair else 1)
+        layer = synth.make_layer(H, I, dt, cuda_device, 7, 0.5)
+        nw = (1.0 + 0.1 * torch.randn(H, device=cuda_device)).to(dt)
+        tol = 1e-6 if dt == torch.float32 else 5e-3
+        for seed in (11, 12):
+            x = synth.make_x(1, H, dt, cuda_device, seed)
+            plain, _ = run_and_check(x, layer.wg, layer.wu, layer.wdt, layer.threshold,
+                                     f"single layer, pair={pair}")
+            r = (0.5 * torch.randn(1, H, device=cuda_device)).to(dt)
+            r_exp = r.float() + plain.reshape(1, H).float()
+            xn = torch.empty(1, H, dtype=dt, device=cuda_device)
+            ops.mlp(x, layer.wg, layer.wu, layer.wdt, layer.threshold, resid=r, x_next=xn,
+                    norm_weight=nw, eps=1e-5)
+            torch.cuda.synchronize()
+            assert O.rel_l2(to_np(r), to_np(r_exp)) <= tol, (seed, "resid")
+            rr = r.float()
+            y = (rr * torch.rsqrt(rr.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dt)
+            assert O.rel_l2(to_np(xn), to_np(nw.float() * y.float())) <= tol, (seed, "x_next")
+    finally:
+        assert L.cats_set_option(b"single_pair", 1) == 0
 
 
 @pytest.mark.parametrize("B", [8, 16])
