@@ -87,7 +87,7 @@ int cats_sm_count(void);
  * active neurons of its own rows (no list barrier) instead of a balanced share.  "l2_ahead_kb"
  * (default 128, 0 = off): how many KiB of its coming gate rows a CTA of the persistent kernel asks
  * into L2 when its copy ring has stood still for about two microseconds (the consumers are at a
- * grid barrier then and HBM would idle).  The same values are read
+ * grid barrier then and HBM would idle); not used by cats_tp_mlp_stack.  The same values are read
  * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
  * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS, CATS_B200_WAIT_MS
  * CATS_B200_XCHG, CATS_B200_LOCAL_LISTS, CATS_B200_L2_AHEAD_KB and CATS_B200_SINGLE_PAIR.
