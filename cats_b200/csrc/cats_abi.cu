@@ -100,6 +100,7 @@ struct Options {
   int use_tma = 1;     // TMA-fed kernels where the shape allows (else the direct-load kernels)
   int ring_kb = 200;   // shared-memory ring per TMA kernel
   int use_mega = 1;    // persistent cooperative kernel for cats_mlp / cats_mlp_stack
+  int pair_ahead_rows = 16; // up-projection rows per segment that stage 1 of cats_mlp asks into L2
   int single_pair = 1; // cats_mlp with one token: the stage-1 / stage-2+3 kernel pair instead
   int bulk_flush = 1;  // persistent kernel: flush accumulators with TMA bulk reduces
   int mma_dot = 1;     // persistent kernel: gate / up dot products on the tensor cores (16-bit)
@@ -118,6 +119,7 @@ Options& options() {
     if (const char* e = getenv("CATS_B200_PDL")) g_use_pdl = atoi(e);
     if (const char* e = getenv("CATS_B200_MEGA")) v.use_mega = atoi(e);
     if (const char* e = getenv("CATS_B200_SINGLE_PAIR")) v.single_pair = atoi(e);
+    if (const char* e = getenv("CATS_B200_PAIR_AHEAD_ROWS")) v.pair_ahead_rows = atoi(e);
     if (const char* e = getenv("CATS_B200_BULK_FLUSH")) v.bulk_flush = atoi(e);
     if (const char* e = getenv("CATS_B200_MMA_DOT")) v.mma_dot = atoi(e);
     if (const char* e = getenv("CATS_B200_PARTS")) v.parts = atoi(e);
@@ -365,8 +367,13 @@ DensePlan plan_dense(int B, int H, int I, int dtype) {
 }
 
 cudaError_t do_gate(const void* x, const void* Wg, WsPtrs ws, int B, int H, int I, int dtype,
-                    float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st) {
-  const TmaPlan p = plan_gate_tma(B, H, I, dtype);
+                    float thr, void* gate_dense, uint8_t* flag_dense, cudaStream_t st,
+                    const void* Wu_ahead = nullptr) {
+  TmaPlan p = plan_gate_tma(B, H, I, dtype);
+  if (Wu_ahead && options().pair_ahead_rows > 0) {
+    p.pf_base = Wu_ahead;
+    p.pf_n = options().pair_ahead_rows;
+  }
   if (p.ok) CATS_DISPATCH(dtype, inst_gate_tma, p, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
   CATS_DISPATCH(dtype, inst_gate, x, Wg, ws, B, H, I, thr, gate_dense, flag_dense, st);
 }
@@ -429,6 +436,7 @@ int cats_set_option(const char* name, int value) {
   else if (!strcmp(name, "pdl")) g_use_pdl = value;
   else if (!strcmp(name, "mega")) options().use_mega = value;
   else if (!strcmp(name, "single_pair")) options().single_pair = value;
+  else if (!strcmp(name, "pair_ahead_rows")) options().pair_ahead_rows = value;
   else if (!strcmp(name, "bulk_flush")) options().bulk_flush = value;
   else if (!strcmp(name, "mma_dot")) options().mma_dot = value;
   else if (!strcmp(name, "parts")) options().parts = value;
@@ -553,7 +561,7 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
       return cuda_status(do_mega(mp, P, A, p, dtype, st));
     }
   }
-  cudaError_t e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st);
+  cudaError_t e = do_gate(x, Wg, p, B, H, I, dtype, threshold, nullptr, nullptr, st, Wu);
   if (e != cudaSuccess) return cuda_status(e);
   return cuda_status(do_updown(3, x, Wu, WdT, p, B, H, I, dtype, out, out_mode, resid, x_next,
                                norm_weight, eps, nullptr, st));

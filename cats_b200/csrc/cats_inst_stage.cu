@@ -57,7 +57,7 @@ cudaError_t run_gate_tma_v(const TmaPlan& p, const void* x, const void* Wg, WsPt
                            cudaStream_t st) {
   return launch(k_gate_tma<T, BT, SR, XS>, dim3(p.grid), dim3(kConsumerThreads + 32 * p.pw), p.smem, st,
                 (const T*)x, (const T*)Wg, ws, B, H, I, thr, (T*)gate_dense, flag_dense, p.S,
-                p.cw, p.rmax, p.wait_kc);
+                p.cw, p.rmax, p.wait_kc, (const T*)p.pf_base, p.pf_n);
 }
 
 template <typename T, int BT>

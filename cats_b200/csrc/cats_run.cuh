@@ -66,6 +66,10 @@ struct TmaPlan {
   int S = 0, grid = 0, sr = 1, nvt = 1, cap = 0, rmax = 0, cw = 1, pw = 1;
   int wait_kc = 0;  // limit of every wait in the kernel, in units of 1024 clock cycles
   size_t smem = 0;
+  // stage 1 only: rows of this matrix (the up projection) to ask into L2 for the first pf_n active
+  // neurons of every segment, for the stage-2 kernel that follows (null: none)
+  const void* pf_base = nullptr;
+  int pf_n = 0;
 };
 
 

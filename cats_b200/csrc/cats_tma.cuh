@@ -348,7 +348,7 @@ template <typename T, int BT, int SR, bool XS>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, int H, int I,
            float thr, T* __restrict__ gate_dense, uint8_t* __restrict__ flag_dense, int S,
-           int cw, int rmax, int wait_kc) {
+           int cw, int rmax, int wait_kc, const T* __restrict__ pf_base, int pf_n) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_ctl[2];  // abort flag, wait limit
   int& s_abort = s_ctl[0];
@@ -462,8 +462,13 @@ k_gate_tma(const T* __restrict__ x, const T* __restrict__ Wg, WsPtrs ws, int B, 
       }
       const unsigned m = __ballot_sync(0xffffffffu, any);
       if (any) {
-        const int pos = r0 + base + __popc(m & ((1u << lane) - 1u));
+        const int rank = base + __popc(m & ((1u << lane) - 1u));
+        const int pos = r0 + rank;
         ws.seg_idx[pos] = r0 + lr;
+        // The stage-2 kernel of CTA c starts with (about) this segment's first active neurons,
+        // and between this point and its first copy HBM idles (this grid's tail, the launch,
+        // counts -> scan -> list): have their up-projection rows brought into L2 meanwhile.
+        if (pf_base && rank < pf_n) l2_prefetch(pf_base + (size_t)(r0 + lr) * H, row_bytes);
 #pragma unroll
         for (int t = 0; t < BT; ++t)
           if (t < B) ws.seg_gate[(size_t)pos * B + t] = v[t];

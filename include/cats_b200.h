@@ -73,7 +73,9 @@ int cats_sm_count(void);
  * (0/1, default 1): cats_mlp with ONE token launches the stage-1 / stage-2+3 kernel pair with
  * programmatic dependent launch instead of the (cooperative) persistent kernel - between other
  * kernels of a stream, as in a decoder, the pair is the faster of the two; cats_mlp_stack is not
- * affected.  Inside the
+ * affected.  "pair_ahead_rows" (default 16, 0 = off): in that pair, stage 1 asks the up-projection
+ * rows of each segment's first active neurons into L2 for the stage-2 kernel, whose first copies
+ * would otherwise wait for HBM after an idle gap.  Inside the
  * persistent kernel: "bulk_flush" (0/1, default 1: accumulators leave through TMA bulk reduces),
  * "mma_dot" (0/1, default 1: tensor-core dot products for batches of 2-4 with 16-bit weights),
  * "parts" (0 = automatic, or 1..3 parts per layer).  "wait_ms": limit of every wait inside a
@@ -90,7 +92,7 @@ int cats_sm_count(void);
  * grid barrier then and HBM would idle); not used by cats_tp_mlp_stack.  The same values are read
  * once from the environment variables CATS_B200_TMA, CATS_B200_RING_KB, CATS_B200_PDL,
  * CATS_B200_MEGA, CATS_B200_BULK_FLUSH, CATS_B200_MMA_DOT, CATS_B200_PARTS, CATS_B200_WAIT_MS
- * CATS_B200_XCHG, CATS_B200_LOCAL_LISTS, CATS_B200_L2_AHEAD_KB and CATS_B200_SINGLE_PAIR.
+ * CATS_B200_XCHG, CATS_B200_LOCAL_LISTS, CATS_B200_L2_AHEAD_KB, CATS_B200_SINGLE_PAIR and CATS_B200_PAIR_AHEAD_ROWS.
  * No reference counterpart (the reference has no device-side waits; its error path is exit(-1),
  * flash_gemv/csrc/cuda/fuse_gemv_cmp_cuda.cu:25-33, 2397-2400).
  */
