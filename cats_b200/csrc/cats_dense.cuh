@@ -213,7 +213,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
   const unsigned dbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_DBAR_BASE));
   const int par0 = __ldcg(ws.hdr + HDR_DLAUNCH) & 1;
   // barrier n (1..4) of layer l
-  auto dtarget = [&](int l, int n) { return dbase + (unsigned)(4 * l + n) * 4u * (unsigned)G; };
+  auto dtarget = [&](int l, int n) { return dbase + (unsigned)(4 * l + n) * (unsigned)G; };
   auto maps = [&](int l) -> const DenseLayerMaps* { return STACK ? &Pg->m[l] : &M1; };
 
   if (tid == 0) {
@@ -405,6 +405,18 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
     const int own_lo = (int)(((long long)ngrp * c) / G), own_hi = (int)(((long long)ngrp * (c + 1)) / G);
     const int own_n = own_hi - own_lo;
     T* x_io = reinterpret_cast<T*>(tail.x_next);   // (stacks: the caller passes x_io here)
+    // Grid barriers of the epilogue warps: ONE arrival and one poller per CTA (the four warps
+    // meet at their named barrier first), so a barrier is 148 adds to one address, not 592.
+    // Every epilogue thread calls these the same number of times whatever happened before.
+    auto ep_arrive = [&]() {
+      epilogue_bar_sync();
+      if (et == 0 && !s_abort) grid_arrive(dbar);
+    };
+    auto ep_wait = [&](unsigned target) {
+      if (et == 0 && !s_abort) grid_wait(dbar, target, &s_abort);
+      epilogue_bar_sync();
+      return !s_abort;
+    };
     for (int l = 0; l < L; ++l) {
       const bool last = l + 1 == L;
       const float thr = STACK ? __ldg(&Pg->thr[l]) : thr1;
@@ -438,8 +450,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * buf);
       }
-      __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 1
+      ep_arrive();                                   // barrier 1
       // ---- phase 2: partial sums into the fp32 accumulators, one row tile at a time
       for (int m_cur = m_first; m_cur <= m_last; ++m_cur, ++seg) {
         const int buf = seg & 1;
@@ -457,10 +468,8 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(acc_empty_u + 8u * (2 + buf));
       }
-      __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 2
-      if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(l, 2), &s_abort);        // one poller per warp
-      ok = __all_sync(0xffffffffu, ok);
+      ep_arrive();                                   // barrier 2
+      ok = ep_wait(dtarget(l, 2)) && ok;
       // ---- tail, this CTA's slice of the columns (groups of four), all tokens
       T* out = last ? reinterpret_cast<T*>(tail.out) : nullptr;
       const int out_mode = last ? tail.out_mode : 0;
@@ -510,11 +519,9 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
         epilogue_bar_sync();
         if (et < B && ok) atomicAdd(ss_cur + et, s_ss[et]);
       }
-      __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 3
+      ep_arrive();                                   // barrier 3
       if (want_norm) {
-        if (lane == 0 && ok) ok = grid_wait(dbar, dtarget(l, 3), &s_abort);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = ep_wait(dtarget(l, 3)) && ok;
         for (int e = et; e < B * own_n && ok; e += 128) {
           const int b = e / own_n, g = own_lo + (e - b * own_n);
           const float rsq = rsqrtf(__ldcg(ss_cur + b) / (float)H + eps);
@@ -527,8 +534,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
           }
         }
       }
-      __syncwarp();
-      if (lane == 0 && ok) grid_arrive(dbar);                                   // barrier 4
+      ep_arrive();                                   // barrier 4
     }
     if (lane == 0) s_count[q] = my_count;
   }
@@ -541,7 +547,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
       atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_DENSE);
     } else if (c == 0) {
       ws.hdr[HDR_NSEG] = G;
-      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + (unsigned)(16 * L) * (unsigned)G);
+      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + (unsigned)(4 * L) * (unsigned)G);
       ws.hdr[HDR_DLAUNCH] = (par0 + L) & 1;
     }
   }

@@ -55,7 +55,7 @@ enum { STATUS_WAIT_TIMEOUT_MEGA = 3 };
 // needs every CTA's down rows of layer l, which need every part's list of layer l: so one counter
 // per part is safe, while one counter shared by the parts is not (a fast CTA's arrival for part
 // h+1 would be counted towards part h while a slow CTA has not published yet).  The layer
-// barrier (one arrival per consumer warp) has its own counter.  The *_BASE slots hold the
+// barrier (one arrival per CTA) has its own counter.  The *_BASE slots hold the
 // counters' values at the start of the current launch.
 enum { HDR_GBAR = 8 /* [kParts] */, HDR_OBAR = 12, HDR_GBAR_BASE = 13, HDR_OBAR_BASE = 14 };
 static_assert(HDR_GBAR + kParts <= HDR_OBAR, "one list-barrier counter per part");
@@ -251,10 +251,10 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
   const unsigned gbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_GBAR_BASE));
   const unsigned obase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_OBAR_BASE));
   // list barrier of (l, h): counter h, G arrivals per layer; layer barrier idx = l, final = L
-  // (kConsumerWarps * G arrivals: every consumer warp arrives for itself)
+  // (G arrivals: one per CTA, after its consumer warps have met)
   auto gtarget = [&](int l) { return gbase + (unsigned)(l + 1) * (unsigned)G; };
   auto otarget = [&](int idx) {
-    return obase + (unsigned)(idx + 1) * (unsigned)(G * kConsumerWarps);
+    return obase + (unsigned)(idx + 1) * (unsigned)G;
   };
 
   // tensor-parallel exchange (K == 0: single GPU)
@@ -1019,16 +1019,20 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           }
         }
       }
-      // every warp publishes its own share of the sums: no CTA barrier, one fence per warp
-      __syncwarp();
-      if (lane == 0 && ok) grid_arrive(obar);
+      // ONE arrival per CTA (the warps meet first): 148 adds to the barrier word per layer
+      // instead of one per consumer warp - adds to one address serialise in L2, and the last
+      // of them is on the layer's critical path
+      consumer_bar_sync();
+      if (tid == 0 && !s_abort) grid_arrive(obar);
     }
 
     next_x(L - 1, true);
     // everyone has read the last layer's accumulators once the final barrier completes
-    __syncwarp();
-    if (lane == 0 && ok) grid_arrive(obar);
-    if (tid == 0 && ok) grid_wait(obar, otarget(L), &s_abort);
+    consumer_bar_sync();
+    if (tid == 0 && !s_abort) {
+      grid_arrive(obar);
+      grid_wait(obar, otarget(L), &s_abort);
+    }
     consumer_bar_sync();
     if (!s_abort) {
       if (!K) {
@@ -1044,7 +1048,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         }
         // (with local lists nobody arrived at the list barriers: their counters did not move)
         ws.hdr[HDR_GBAR_BASE] = (int)(gbase + (A.local ? 0u : (unsigned)L * (unsigned)G));
-        ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)(G * kConsumerWarps));
+        ws.hdr[HDR_OBAR_BASE] = (int)(obase + (unsigned)(L + 1) * (unsigned)G);
         // segment counts are per part (not a flat list); with local lists they are this layer's
         // per-CTA counts and add up to the number of active neurons
         ws.hdr[HDR_NSEG] = A.local ? G : -1;
