@@ -1021,7 +1021,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       }
       // ONE arrival per CTA (the warps meet first): 148 adds to the barrier word per layer
       // instead of one per consumer warp - adds to one address serialise in L2, and the last
-      // of them is on the layer's critical path
+      // of them is on the layer's critical path (measured: 41.1 against 41.4 us per layer)
       consumer_bar_sync();
       if (tid == 0 && !s_abort) grid_arrive(obar);
     }
