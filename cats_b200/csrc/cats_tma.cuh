@@ -639,7 +639,15 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
       __syncwarp();
       if (lane < nb) mbar_arrive(empty_u + 8u * my_slot);
     }
-    if (cnt > 0) {
+    // The CTA's partial sums leave through the ring, which is idle now (every row has been
+    // consumed): fp32 [B, H] staged in shared memory, then ONE bulk reduce-add per token into
+    // the accumulators (one request per 128 bytes at L2) instead of a 16-byte red per thread
+    // and vector - 148 CTAs adding to the same 16 KB serialise there.  Falls back to the reds
+    // where the ring is smaller than B * H floats.
+    const bool bulk = (size_t)S * row_bytes >= (size_t)B * H * sizeof(float);
+    consumer_bar_sync();  // every warp has read its columns of the last rows: the ring is free
+    if (cnt > 0 && ok) {
+      float* stg = reinterpret_cast<float*>(ring);
 #pragma unroll
       for (int g = 0; g < NVT; ++g) {
         const int v = g * kConsumerThreads + tid;
@@ -647,15 +655,29 @@ k_updown_tma(const T* __restrict__ x, const T* __restrict__ Wu, const T* __restr
 #pragma unroll
           for (int t = 0; t < BT; ++t) {
             if (t < B) {
-              float* dst = ws.acc32 + (size_t)t * H + (size_t)v * N;
+              float* dst = (bulk ? stg : ws.acc32) + (size_t)t * H + (size_t)v * N;
 #pragma unroll
-              for (int i = 0; i < N; i += 4)
-                red_add_v4(dst + i, acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2],
-                           acc[g][t][i + 3]);
+              for (int i = 0; i < N; i += 4) {
+                if (bulk)
+                  *reinterpret_cast<float4*>(dst + i) =
+                      make_float4(acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2], acc[g][t][i + 3]);
+                else
+                  red_add_v4(dst + i, acc[g][t][i], acc[g][t][i + 1], acc[g][t][i + 2],
+                             acc[g][t][i + 3]);
+              }
             }
           }
         }
       }
+      if (bulk) fence_proxy_async_smem();
+    }
+    consumer_bar_sync();  // the staged sums are complete
+    if (bulk && tid == 0 && cnt > 0 && !s_abort) {
+      for (int t = 0; t < B; ++t)
+        bulk_reduce_add_f32(ws.acc32 + (size_t)t * H, ring_u + (uint32_t)t * H * (uint32_t)sizeof(float),
+                            (uint32_t)H * (uint32_t)sizeof(float));
+      bulk_commit();
+      bulk_wait_all();
     }
   }
 
