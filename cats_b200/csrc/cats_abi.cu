@@ -346,10 +346,11 @@ bool single_layer_pair(int B, int H, int I, int dtype) {
 // 70B shape), rings as deep as shared memory allows.
 DensePlan plan_dense(int B, int H, int I, int dtype) {
   DensePlan p;
-  if (dtype == CATS_F32 || B < 1 || B > 16 || H % 128 || I % 64 || H < 128) return p;
+  // (H <= 8192: the tail keeps a token's row in the registers of 128 threads)
+  if (dtype == CATS_F32 || B < 1 || B > 16 || H % 128 || I % 64 || H < 128 || H > 8192) return p;
   p.grid = dev_info().sms;
   if (p.grid > I / 8) p.grid = I / 8;
-  if (p.grid < 1) return p;
+  if (p.grid < B) return p;                              // CTA b finishes token b
   const int rows = (I + p.grid - 1) / p.grid;            // most neurons any CTA owns
   const int tiles = (rows + 127) / 128;
   const int per_tile = (rows + tiles - 1) / tiles;

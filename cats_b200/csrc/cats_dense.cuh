@@ -118,28 +118,27 @@ template <> struct UmmaFmt<__nv_bfloat16> { static constexpr int v = 1; };
 //   phase 2  stage = [Wd block][Wd block][h block][h block]: split-K - the (128-row tile of H) x
 //            (64-column step of I) blocks of Wd [H, I] are dealt out evenly over the CTAs in
 //            order; partial sums leave TMEM through fp32 reductions into the workspace.
-//   tail     spread over all CTAs: every CTA turns its slice of the columns into out / the new
-//            residual and adds its part of each token's sum of squares, then writes its slice of
-//            x_next = rmsnorm(resid) (times the norm weight, if given).
-// Four grid barriers order a layer (one monotonic counter in the workspace header, four
-// arrivals per CTA and barrier - one per epilogue warp; its value at launch in the next slot):
+//   tail     token b is finished by CTA b alone: out / the new residual, the token's sum of
+//            squares (a sum inside one CTA: no grid barrier for it), x_next = rmsnorm(resid)
+//            (times the norm weight, if given), and the token's accumulator row cleared.
+// Three grid barriers order a layer (one monotonic counter in the workspace header, ONE arrival
+// per CTA and barrier - the epilogue warps meet first; its value at launch in the next slot):
 //   1 every CTA's h is written        2 every CTA's partial sums are added
-//   3 the sums of squares are complete  4 every CTA's slice of x_next is written
+//   3 every token's x_next is written (and its accumulators are clear again)
 // A stage's weight blocks never depend on a barrier, its activation block (x or h) does.  The
 // producer issues weight blocks as far ahead as the ring allows and keeps the stages whose
 // activation block is still owed in a FIFO: the block goes out as soon as its barrier has
 // completed (polled between stages) and at the latest when the ring wraps onto that stage.  So
 // the ring stays full across the h hand-off and across layers; only 2 KB per stage wait.
 // x alternates between two buffers from layer to layer; the last layer writes where the caller
-// asked (x_io for a stack).  The per-token sums of squares alternate between two header arrays,
-// the one the next layer (or launch) will use being cleared meanwhile.
+// asked (x_io for a stack).
 // The producer's and the issuer's bookkeeping is incremental on purpose: each is ONE thread that
 // has to handle a stage every ~0.7 us, and an integer division by a run-time value costs a tenth
 // of that (measured: 3.4 TB/s with a dozen divisions per stage, 6 TB/s without).
 // STACK: the layers' tensor maps and thresholds come from a table in global memory (written by
 // k_dense_table just before); else (one layer) from the kernel parameters.
 // ---------------------------------------------------------------------------------------------
-enum { HDR_DBAR = 16, HDR_DBAR_BASE = 17, HDR_DLAUNCH = 18, HDR_DSS = 32 /* [2][16] floats */ };
+enum { HDR_DBAR = 16, HDR_DBAR_BASE = 17 };
 constexpr uint32_t kDenseStage = 2 * kDenseATile + 4096;   // 36 KB, both phases
 constexpr int kDenseMaxLayers = 80;   // 80 x three 128-byte maps + thresholds in one 32 KB launch
 struct DenseLayerMaps {
@@ -183,7 +182,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
   __shared__ uint64_t s_bars[2 * 16 + 8];
   __shared__ uint32_t s_tmem;
   __shared__ int s_count[4];
-  __shared__ float s_ss[16];
+  __shared__ float s_ss[1];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, c = blockIdx.x;
@@ -211,9 +210,8 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
 
   unsigned* dbar = reinterpret_cast<unsigned*>(ws.hdr + HDR_DBAR);
   const unsigned dbase = __ldcg(reinterpret_cast<const unsigned*>(ws.hdr + HDR_DBAR_BASE));
-  const int par0 = __ldcg(ws.hdr + HDR_DLAUNCH) & 1;
   // barrier n (1..4) of layer l
-  auto dtarget = [&](int l, int n) { return dbase + (unsigned)(4 * l + n) * (unsigned)G; };
+  auto dtarget = [&](int l, int n) { return dbase + (unsigned)(3 * l + n) * (unsigned)G; };
   auto maps = [&](int l) -> const DenseLayerMaps* { return STACK ? &Pg->m[l] : &M1; };
 
   if (tid == 0) {
@@ -263,7 +261,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
       // the barrier a stage's activation block waits for (0: none)
       auto needs = [&](const Cur& q) {
         if (q.r >= n1) return dtarget(q.l, 1);
-        return q.l ? dtarget(q.l - 1, 4) : 0u;
+        return q.l ? dtarget(q.l - 1, 3) : 0u;
       };
       auto act_block = [&](const Cur& q) {
         const uint32_t st = ring_u + (uint32_t)q.s * kDenseStage + 2 * kDenseATile, bar = full_u + 8u * q.s;
@@ -402,8 +400,6 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
     bool ok = true;
     int my_count = 0, tcount = 0, seg = 0;
     const int ngrp = H >> 2;
-    const int own_lo = (int)(((long long)ngrp * c) / G), own_hi = (int)(((long long)ngrp * (c + 1)) / G);
-    const int own_n = own_hi - own_lo;
     T* x_io = reinterpret_cast<T*>(tail.x_next);   // (stacks: the caller passes x_io here)
     // Grid barriers of the epilogue warps: ONE arrival and one poller per CTA (the four warps
     // meet at their named barrier first), so a barrier is 148 adds to one address, not 592.
@@ -470,7 +466,9 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
       }
       ep_arrive();                                   // barrier 2
       ok = ep_wait(dtarget(l, 2)) && ok;
-      // ---- tail, this CTA's slice of the columns (groups of four), all tokens
+      // ---- tail: token b is finished by CTA b alone (4096-8192 columns are one round of loads
+      // for 128 threads), so its sum of squares is a sum inside one CTA and needs no grid
+      // barrier; the other CTAs go straight to the layer's last barrier
       T* out = last ? reinterpret_cast<T*>(tail.out) : nullptr;
       const int out_mode = last ? tail.out_mode : 0;
       T* resid = reinterpret_cast<T*>(tail.resid);
@@ -478,63 +476,91 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
       T* xn = last ? reinterpret_cast<T*>(tail.x_next) : ((l & 1) ? x_io : x_tmp);
       const T* norm_w = last ? reinterpret_cast<const T*>(tail.norm_w) : nullptr;
       const bool want_norm = resid != nullptr && xn != nullptr && out_mode != 1;
-      const int par = (par0 + l) & 1;
-      float* ss_cur = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + par * 16;
-      float* ss_nxt = reinterpret_cast<float*>(ws.hdr + HDR_DSS) + (par ^ 1) * 16;
-      if (c == 0 && et < 16) ss_nxt[et] = 0.f;         // for the next layer / launch
-      if (et < 16) s_ss[et] = 0.f;
+      const bool mine = c < B;                 // (the host makes sure the grid has B CTAs)
+      if (et == 0) s_ss[0] = 0.f;
       epilogue_bar_sync();
-      for (int e = et; e < B * own_n && ok; e += 128) {
-        const int b = e / own_n, g = own_lo + (e - b * own_n);
-        float4* ap = reinterpret_cast<float4*>(ws.acc32 + (size_t)b * H) + g;
-        const float4 a = __ldcg(ap);
-        *ap = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float v[4] = {a.x, a.y, a.z, a.w};
-        const size_t o = (size_t)b * H + 4 * (size_t)g;
-        if (out_mode == 1) {
-          float* of = reinterpret_cast<float*>(out) + o;
+      // Every thread owns up to kTailG groups of four columns (H <= 8192) and fetches all of them
+      // before it uses any: one round trip to L2 instead of one per group.  The new residual
+      // stays in registers for the second pass.
+      constexpr int kTailG = 16;
+      union Pack { uint2 u; T e[4]; };
+      Pack rr[kTailG];
+      if (mine && ok) {
+        float4 av[kTailG];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) of[i] += v[i];
-        } else {
-          if (out) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) out[o + i] = V::from_f(v[i]);
+        for (int k = 0; k < kTailG; ++k) {
+          const int g = et + 128 * k;
+          if (g < ngrp) {
+            av[k] = __ldcg(reinterpret_cast<const float4*>(ws.acc32 + (size_t)c * H) + g);
+            if (resid && out_mode != 1)
+              rr[k].u = *reinterpret_cast<const uint2*>(resid + (size_t)c * H + 4 * (size_t)g);
           }
-          if (resid) {
-            float ssq = 0.f;
+        }
+        float ssq = 0.f;
+#pragma unroll
+        for (int k = 0; k < kTailG; ++k) {
+          const int g = et + 128 * k;
+          if (g < ngrp) {
+            reinterpret_cast<float4*>(ws.acc32 + (size_t)c * H)[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float v[4] = {av[k].x, av[k].y, av[k].z, av[k].w};
+            const size_t o = (size_t)c * H + 4 * (size_t)g;
+            if (out_mode == 1) {
+              float4* of = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o);
+              float4 t = *of;
+              t.x += v[0]; t.y += v[1]; t.z += v[2]; t.w += v[3];
+              *of = t;
+            } else {
+              if (out) {
+                Pack po;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) po.e[i] = V::from_f(v[i]);
+                *reinterpret_cast<uint2*>(out + o) = po.u;
+              }
+              if (resid) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const T rn = V::from_f(V::to_f(rr[k].e[i]) + v[i]);
+                  rr[k].e[i] = rn;
+                  const float rf = V::to_f(rn);
+                  ssq = fmaf(rf, rf, ssq);
+                }
+                *reinterpret_cast<uint2*>(resid + o) = rr[k].u;
+              }
+            }
+          }
+        }
+        if (want_norm) {
+          ssq = warp_sum(ssq);
+          if (lane == 0) atomicAdd(&s_ss[0], ssq);
+        }
+      }
+      epilogue_bar_sync();
+      if (mine && ok && want_norm) {
+        const float rsq = rsqrtf(s_ss[0] / (float)H + eps);
+        Pack nw[kTailG];
+        if (norm_w) {
+#pragma unroll
+          for (int k = 0; k < kTailG; ++k) {
+            const int g = et + 128 * k;
+            if (g < ngrp) nw[k].u = *reinterpret_cast<const uint2*>(norm_w + 4 * (size_t)g);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < kTailG; ++k) {
+          const int g = et + 128 * k;
+          if (g < ngrp) {
+            Pack py;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const T rn = V::from_f(V::to_f(resid[o + i]) + v[i]);
-              resid[o + i] = rn;
-              const float rf = V::to_f(rn);
-              ssq = fmaf(rf, rf, ssq);
+              T y = V::from_f(V::to_f(rr[k].e[i]) * rsq);
+              if (norm_w) y = V::from_f(V::to_f(nw[k].e[i]) * V::to_f(y));
+              py.e[i] = y;
             }
-            if (want_norm) atomicAdd(&s_ss[b], ssq);   // per CTA in shared memory first
+            *reinterpret_cast<uint2*>(xn + (size_t)c * H + 4 * (size_t)g) = py.u;
           }
         }
       }
-      if (want_norm) {
-        // one global add per CTA and token: thousands of adds to the same few addresses would
-        // serialise in L2
-        epilogue_bar_sync();
-        if (et < B && ok) atomicAdd(ss_cur + et, s_ss[et]);
-      }
-      ep_arrive();                                   // barrier 3
-      if (want_norm) {
-        ok = ep_wait(dtarget(l, 3)) && ok;
-        for (int e = et; e < B * own_n && ok; e += 128) {
-          const int b = e / own_n, g = own_lo + (e - b * own_n);
-          const float rsq = rsqrtf(__ldcg(ss_cur + b) / (float)H + eps);
-          const size_t o = (size_t)b * H + 4 * (size_t)g;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            T y = V::from_f(V::to_f(resid[o + i]) * rsq);
-            if (norm_w) y = V::from_f(V::to_f(norm_w[4 * g + i]) * V::to_f(y));
-            xn[o + i] = y;
-          }
-        }
-      }
-      ep_arrive();                                   // barrier 4
+      ep_arrive();                                   // barrier 3: x_{l+1} and the clean accumulators
     }
     if (lane == 0) s_count[q] = my_count;
   }
@@ -547,8 +573,7 @@ k_dense(const DenseStackParams* __restrict__ Pg, const __grid_constant__ DenseLa
       atomicMax(ws.hdr + HDR_STATUS, STATUS_WAIT_TIMEOUT_DENSE);
     } else if (c == 0) {
       ws.hdr[HDR_NSEG] = G;
-      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + (unsigned)(4 * L) * (unsigned)G);
-      ws.hdr[HDR_DLAUNCH] = (par0 + L) & 1;
+      ws.hdr[HDR_DBAR_BASE] = (int)(dbase + (unsigned)(3 * L) * (unsigned)G);
     }
   }
   if (s_abort) drain_after_abort();
