@@ -316,7 +316,7 @@ def use_dense(B: int, sparsity: Optional[float] = None, union_density: Optional[
 
 
 def dense_supported(B: int, H: int, I: int, dtype: torch.dtype) -> bool:
-    """Whether ``mlp_dense`` can run this shape (16-bit weights, H % 128 == 0, I % 64 == 0)."""
+    """Whether ``mlp_dense`` can run this shape (16-bit weights, H % 128 == 0, H <= 8192, I % 64 == 0)."""
     if dtype not in (torch.float16, torch.bfloat16):
         return False
     return _lib.lib().cats_dense_supported(B, H, I, dtype_code(dtype)) == 1

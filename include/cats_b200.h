@@ -190,8 +190,8 @@ int cats_mlp(const void* x, const void* Wg, const void* Wu, const void* WdT, voi
  * path for one token and for batches with strongly overlapping masks.
  *   Wd [H, I]: down_proj.weight as nn.Linear stores it, the layout flag_gemv_gemv_inner* receive
  *   (flash_gemv/flash_gemv/flash_gemv.py:36-43); Wg, Wu [I, H]; everything else as for cats_mlp.
- * fp16 / bf16 only (fp32 weights would have to go through tf32), H a multiple of 128, I a
- * multiple of 64, B <= 16: otherwise CATS_ERR_MODE (cats_dense_supported tells beforehand) and the
+ * fp16 / bf16 only (fp32 weights would have to go through tf32), H a multiple of 128 and at most
+ * 8192, I a multiple of 64 (and at least 8 * B), B <= 16: otherwise CATS_ERR_MODE (cats_dense_supported tells beforehand) and the
  * caller uses cats_mlp.  gate * up is rounded to the storage type between the two GEMMs, as the
  * reference's stage 2 hands it to its stage 3.
  * Replaces the B in {2, 8, 16} launches of flag_gemv_gemv_inner* (fuse_gemv_cmp_cuda.cu:2368-2400).
