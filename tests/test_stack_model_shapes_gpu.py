@@ -135,6 +135,38 @@ def test_both_single_layer_routes_at_model_shape(H, I, dt, pair, cuda_device):
         assert L.cats_set_option(b"single_pair", 1) == 0
 
 
+def test_look_ahead_options_do_not_change_results(cuda_device):
+    """The L2 look-ahead of the persistent kernel's producers and the one stage 1 does for the
+    kernel pair only move bytes earlier: with them off, the results are the same bits for the
+    stack (same kernel, same order of every sum per CTA; split-K order aside) within the fp32
+    bound, and the pair's output within it too."""
+    from cats_b200 import _lib, ops, synth
+    from cats_b200.stack import CatsMLPStack
+
+    L = _lib.lib()
+    H, I, dt = 4096, 14336, torch.float32
+    layers = synth.make_stack(2, H, I, dt, cuda_device, 23, 0.5)
+    x0 = synth.make_x(1, H, dt, cuda_device, 9).reshape(1, H)
+    results = {}
+    try:
+        for on in (1, 0):
+            assert L.cats_set_option(b"l2_ahead_kb", 128 if on else 0) == 0
+            assert L.cats_set_option(b"pair_ahead_rows", 16 if on else 0) == 0
+            stack = CatsMLPStack(layers, batch=1, dense=False)
+            stack.set_input(x0)
+            stack.run_device()
+            y = ops.mlp(x0.reshape(1, 1, H), layers[0].wg, layers[0].wu, layers[0].wdt,
+                        layers[0].threshold)
+            torch.cuda.synchronize()
+            assert stack.ws.counters()[1] == 0
+            results[on] = (to_np(stack.resid), to_np(stack.x), to_np(y))
+    finally:
+        assert L.cats_set_option(b"l2_ahead_kb", 128) == 0
+        assert L.cats_set_option(b"pair_ahead_rows", 16) == 0
+    for a, b in zip(results[1], results[0]):
+        assert O.rel_l2(a, b) <= 1e-5
+
+
 @pytest.mark.parametrize("B", [8, 16])
 def test_large_batches_at_model_shape(B, cuda_device):
     """The sparse kernels' own path for batches beyond four (direct loads): kept correct although
