@@ -47,9 +47,10 @@ WORKLOADS = {
 }
 # (dram__bytes_read + dram__bytes_write) / algorithmic bytes of k_cats_mega for the default
 # workload, from the ncu capture summarised in profiles/k_cats_mega_mistral7b_fp16_s50_ncu_full.md
-# (2 layers captured: 236.7 MB per layer against 234.8 MB algorithmic; DRAM traffic is the rows a
-# rank streams, so it grows with the layers and with the rows per rank like the algorithmic bytes)
-NCU_TRAFFIC_RATIO = {("mistral7b", 0.5, 1): 236.7e6 / 234.8e6}
+# (4 layers captured: 950.75 MB read + written against 943.95 MB algorithmic; DRAM traffic is the
+# rows a rank streams, so it grows with the layers and with the rows per rank like the
+# algorithmic bytes)
+NCU_TRAFFIC_RATIO = {("mistral7b", 0.5, 1): 950.75e6 / 943.95e6}
 METRIC = "cats_mlp_stack_decode_tokens_per_s"
 UNIT = "tokens/s"
 

@@ -306,10 +306,11 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
       // are known ahead of time (those of the active lists are not), so a producer whose wait
       // for a free stage lasts longer than the ring's ordinary back-pressure asks the next D
       // gate rows into L2 - its share: every npw-th row from the one it is waiting to copy -
-      // and the ring refills from L2 once the barrier has passed.  A producer that waits for a
-      // list does the same with the first rows of the next layer.  Measured at the Mistral-7B
-      // shape: 128 KB per CTA takes 2.6 % off a layer; more is slower again, and prefetching in
-      // the steady state, with every copy, is slower than none.
+      // and the ring refills from L2 once the barrier has passed.  Measured at the Mistral-7B
+      // shape: 128 KB per CTA takes 2.6 % off a layer (for 3-4 % more DRAM reads: part of what
+      // was asked for is fetched again); more is slower again, prefetching in the steady state,
+      // with every copy, is slower than none, and so is asking for the next layer's first rows
+      // while a producer waits for a list.
       const int D = A.pf_rows;
       const long long kStall = 4000;  // cycles, about 2 us (1000 .. 8000 measured alike)
       const int pr0 = seg_lo(0), pR0 = seg_hi(0) - pr0;
@@ -348,7 +349,6 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
         const T* Wg = reinterpret_cast<const T*>(P.wg[l]);
         const T* Wu = reinterpret_cast<const T*>(P.wu[l]);
         const T* Wd = reinterpret_cast<const T*>(P.wdt[l]);
-        const T* Wg_next = (D > 0 && l + 1 < L) ? reinterpret_cast<const T*>(P.wg[l + 1]) : nullptr;
         int g0 = 0;
         for (int h = 0; h < NP && ok; ++h) {
           const int r0 = seg_lo(h), R = seg_hi(h) - r0;
@@ -361,10 +361,7 @@ k_cats_mega(const __grid_constant__ MegaParams P, const MegaArgs A, WsPtrs ws) {
           g0 += R;
         }
         for (int h = 0; h < NP && ok; ++h) {
-          if (!mbar_wait_or(lready_u + 8u * h, l & 1, &s_abort, kStall, [&]() {
-                if (Wg_next)
-                  for (int d = p; d < D; d += npw) prefetch_gate(Wg_next, d);
-              })) {
+          if (!mbar_wait(lready_u + 8u * h, l & 1, &s_abort)) {
             ok = false;
             break;
           }
